@@ -1,0 +1,2 @@
+from .allocator import CacheFull, FreeList
+from .sequence_cache import PAGE_TOKENS, KVLayerView, SequenceCache, StateLayerView, pages_for

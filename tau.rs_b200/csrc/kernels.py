@@ -1,0 +1,254 @@
+"""Python face of the CUDA kernels: checks shapes and dtypes, then launches on the current stream.
+
+Every function here runs a hand-written kernel of this folder; there is no other
+implementation behind them.  If the extension cannot be compiled or loaded, or a tensor is
+not on a CUDA device, the call fails with an error.  Kernels refuse sizes that they do not
+cover instead of computing something else.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+PAGE_TOKENS = 64
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _pointer(tensor: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _code(tensor: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[tensor.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {tensor.dtype} is not supported; use float32 or bfloat16") from None
+
+
+def _require(condition: bool, message: str) -> None:
+    if not condition:
+        raise KernelError(message)
+
+
+def _on_device(*tensors) -> None:
+    for tensor in tensors:
+        if tensor is not None:
+            _require(tensor.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
+            _require(tensor.is_contiguous() or tensor.stride(-1) == 1, "tensors must have a unit innermost stride")
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        library = build.load_library("elementwise.cu")
+        library.tau_error_string.restype = ctypes.c_char_p
+        text = library.tau_error_string(ctypes.c_int(status)).decode()
+        raise KernelError(f"{what} failed: {text} (CUDA error {status})")
+
+
+def _f32_vector(tensor: Optional[torch.Tensor], length: int, what: str) -> None:
+    if tensor is not None:
+        _require(tensor.dtype == torch.float32 and tensor.numel() == length and tensor.is_contiguous(),
+                 f"{what} must be a contiguous float32 vector of {length} elements")
+
+
+def _int_vector(tensor: torch.Tensor, what: str) -> None:
+    _require(tensor.dtype == torch.int32 and tensor.stride(-1) == 1, f"{what} must be int32")
+
+
+# ---------------------------------------------------------------------------- elementwise
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    _on_device(tokens, table, out)
+    _int_vector(tokens, "token ids")
+    _require(table.dtype == out.dtype and table.is_contiguous() and out.is_contiguous(), "table and output must match")
+    _require(out.shape == (tokens.shape[0], table.shape[1]), "output must be [tokens, width]")
+    library = build.load_library("elementwise.cu")
+    _check(library.tau_embedding(_code(table), _pointer(tokens), _pointer(table), _pointer(out), ctypes.c_int(tokens.shape[0]),
+                                 ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), _stream()), "embedding")
+
+
+def rms_norm(values, weight, eps: float, out, rows=None, branch=None) -> None:
+    """`out[i] = norm(round(values[r] + branch[r])) * weight`, `r = rows[i]` or `i`; `values` is not changed."""
+    _on_device(values, weight, out, rows, branch)
+    width = values.shape[-1]
+    _f32_vector(weight, width, "the norm weight")
+    _require(values.is_contiguous() and out.is_contiguous() and out.dtype == values.dtype and out.shape[-1] == width,
+             "norm input and output must be contiguous with the same dtype and width")
+    if branch is not None:
+        _require(branch.shape == values.shape and branch.dtype == values.dtype and branch.is_contiguous(), "branch must match the input")
+    if rows is not None:
+        _int_vector(rows, "row numbers")
+    count = out.numel() // width
+    _require(count == (rows.shape[0] if rows is not None else values.numel() // width), "output row count does not match")
+    library = build.load_library("elementwise.cu")
+    _check(library.tau_rms_norm(_code(values), _pointer(values), _pointer(branch), _pointer(rows), _pointer(weight), _pointer(out),
+                                ctypes.c_int(count), ctypes.c_int(width), ctypes.c_float(eps), _stream()), "rms_norm")
+
+
+def add_rms_norm(branch, residual, weight, eps: float, out) -> None:
+    """`residual = round(residual + branch)` in place; `out = norm(residual) * weight`."""
+    _on_device(branch, residual, weight, out)
+    width = residual.shape[-1]
+    _f32_vector(weight, width, "the norm weight")
+    _require(branch.shape == residual.shape == out.shape and branch.dtype == residual.dtype == out.dtype,
+             "branch, residual and output must match")
+    _require(branch.is_contiguous() and residual.is_contiguous() and out.is_contiguous(), "tensors must be contiguous")
+    library = build.load_library("elementwise.cu")
+    _check(library.tau_add_rms_norm(_code(residual), _pointer(branch), _pointer(residual), _pointer(weight), _pointer(out),
+                                    ctypes.c_int(residual.numel() // width), ctypes.c_int(width), ctypes.c_float(eps), _stream()),
+           "add_rms_norm")
+
+
+def silu_mul(stacked, out) -> None:
+    """`out[r, c] = silu(stacked[r, c]) * stacked[r, width + c]`."""
+    _on_device(stacked, out)
+    width = out.shape[-1]
+    _require(stacked.shape[-1] == 2 * width and stacked.shape[0] == out.shape[0] and stacked.dtype == out.dtype,
+             "input must be [rows, 2 * width] and output [rows, width]")
+    _require(stacked.is_contiguous() and out.is_contiguous(), "tensors must be contiguous")
+    library = build.load_library("elementwise.cu")
+    _check(library.tau_silu_mul(_code(out), _pointer(stacked), _pointer(out), ctypes.c_longlong(out.shape[0]), ctypes.c_int(width),
+                                _stream()), "silu_mul")
+
+
+# ---------------------------------------------------------------------------- products
+def gemm_simt(values, weight, bias, out) -> None:
+    """`out = values @ weight.T + bias` on the 32-bit pipes; any sizes."""
+    _on_device(values, weight, bias, out)
+    rows, depth = values.shape
+    features = weight.shape[0]
+    _require(weight.shape[1] == depth and out.shape == (rows, features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(values.dtype == weight.dtype, "input and weight must have the same dtype")
+    _require(out.dtype == values.dtype or out.dtype == torch.float32, "output must have the input's dtype or float32")
+    _f32_vector(bias, features, "the bias")
+    library = build.load_library("gemm_simt.cu")
+    _check(library.tau_gemm_simt(_code(values), _code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out),
+                                 ctypes.c_int(rows), ctypes.c_int(features), ctypes.c_int(depth),
+                                 ctypes.c_longlong(values.stride(0)), ctypes.c_longlong(weight.stride(0)),
+                                 ctypes.c_longlong(out.stride(0)), _stream()), "gemm_simt")
+
+
+def linear(values, weight, bias, out) -> None:
+    """`out = values @ weight.T + bias` with the kernel that fits the dtype and the sizes."""
+    gemm_simt(values, weight, bias, out)
+
+
+# ---------------------------------------------------------------------------- attention
+def attention_prepare(projected, queries, keys, values, write_cache: bool, q_weight, k_weight, eps: float, cos, sin,
+                      rotary_dim: int, positions, token_seq, page_rows, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Per-head norm and rotation of the projected queries and keys; keys and values go to their cache pages.
+
+    `projected` is `[tokens, (n_heads + 2 n_kv_heads) head_dim]` (only the query part is
+    needed when `write_cache` is false); `queries` receives `[tokens, n_heads head_dim]`.
+    """
+    _on_device(projected, queries, keys, values, q_weight, k_weight, cos, sin, positions, token_seq, page_rows)
+    tokens = projected.shape[0]
+    needed = (n_heads + (2 * n_kv_heads if write_cache else 0)) * head_dim
+    _require(projected.shape[1] >= needed, f"projected rows must hold {needed} elements")
+    _require(queries.shape == (tokens, n_heads * head_dim) and queries.is_contiguous() and queries.dtype == projected.dtype,
+             "queries must be [tokens, n_heads * head_dim]")
+    _require(head_dim % 16 == 0 and 16 <= head_dim <= 256, "head_dim must be a multiple of 16 between 16 and 256")
+    _require(keys.dtype == projected.dtype and values.dtype == projected.dtype, "cache dtype must match the activations")
+    _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
+             and values.shape == keys.shape, "cache pages must be [pages, n_kv_heads, 64, head_dim]")
+    _f32_vector(q_weight, head_dim, "the q norm weight")
+    _f32_vector(k_weight, head_dim, "the k norm weight")
+    if rotary_dim:
+        _require(cos is not None and sin is not None and cos.dtype == torch.float32 and cos.shape == sin.shape
+                 and cos.shape[1] == rotary_dim // 2 and cos.is_contiguous() and sin.is_contiguous(),
+                 "rotation tables must be float32 [positions, rotary_dim / 2]")
+    _int_vector(positions, "positions")
+    _int_vector(token_seq, "token_seq")
+    _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("attention_generic.cu")
+    _check(library.tau_attention_prepare(
+        _code(projected), _pointer(projected), ctypes.c_longlong(projected.stride(0)), _pointer(queries), _pointer(keys), _pointer(values),
+        _pointer(q_weight), _pointer(k_weight), ctypes.c_float(eps), _pointer(cos), _pointer(sin), ctypes.c_int(rotary_dim),
+        _pointer(positions), _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim), ctypes.c_int(1 if write_cache else 0),
+        _stream()), "attention_prepare")
+
+
+def attention_generic(queries, keys, values, out, positions, token_seq, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
+                      scale: float, window: int) -> None:
+    _on_device(queries, keys, values, out, positions, token_seq, page_rows)
+    tokens = queries.shape[0]
+    _require(queries.shape == (tokens, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.is_contiguous()
+             and out.dtype == queries.dtype == keys.dtype == values.dtype, "queries and output must be [tokens, n_heads * head_dim]")
+    _require(head_dim % 16 == 0 and 16 <= head_dim <= 256, "head_dim must be a multiple of 16 between 16 and 256")
+    _require(n_heads % n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads")
+    _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
+             and values.shape == keys.shape, "cache pages must be [pages, n_kv_heads, 64, head_dim]")
+    _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("attention_generic.cu")
+    _check(library.tau_attention_generic(
+        _code(queries), _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(positions), _pointer(token_seq),
+        _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads),
+        ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention")
+
+
+def decode_splits(n_seqs: int, max_len: int) -> int:
+    """Number of context splits that decode attention uses for this many sequences of at most this length."""
+    return 1
+
+
+def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+              window: int) -> None:
+    """Causal attention of the step's tokens over their sequences' cache pages (which hold the step's own keys already)."""
+    attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
+
+
+# ---------------------------------------------------------------------------- selection
+_select_scratch = {}
+
+
+def _scratch_for(logits) -> torch.Tensor:
+    library = build.load_library("sampling.cu")
+    library.tau_select_scratch_words.restype = ctypes.c_longlong
+    words = library.tau_select_scratch_words(ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]))
+    key = (logits.device, torch.cuda.current_stream().cuda_stream)
+    scratch = _select_scratch.get(key)
+    if scratch is None or scratch.numel() < words:
+        scratch = _select_scratch[key] = torch.empty(max(words, 1024), dtype=torch.int32, device=logits.device)
+    return scratch
+
+
+def _check_selection(logits, tokens, valid) -> None:
+    _on_device(logits, tokens, valid)
+    _require(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be contiguous float32 [rows, vocab]")
+    _require(tokens.dtype == torch.int32 and valid.dtype == torch.int32 and tokens.numel() == logits.shape[0] == valid.numel()
+             and tokens.is_contiguous() and valid.is_contiguous(), "tokens and valid must be int32 [rows]")
+
+
+def argmax(logits, tokens, valid) -> None:
+    """Greatest logit of each row (NaN left out, highest id among equals); `valid[r] == 0` if the row is all NaN."""
+    _check_selection(logits, tokens, valid)
+    scratch = _scratch_for(logits)
+    library = build.load_library("sampling.cu")
+    _check(library.tau_argmax(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
+                              ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax")
+
+
+def sample_gumbel(logits, tokens, valid, inverse_temperature: float, seed: int, request_ids, token_indices) -> None:
+    _check_selection(logits, tokens, valid)
+    _on_device(request_ids, token_indices)
+    _int_vector(request_ids, "request ids")
+    _int_vector(token_indices, "token indices")
+    _require(request_ids.numel() == logits.shape[0] == token_indices.numel(), "one request id and token index per row")
+    scratch = _scratch_for(logits)
+    library = build.load_library("sampling.cu")
+    _check(library.tau_sample_gumbel(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
+                                     ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid),
+                                     ctypes.c_float(inverse_temperature), ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF),
+                                     _pointer(request_ids), _pointer(token_indices), _stream()), "sample_gumbel")

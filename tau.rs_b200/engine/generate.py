@@ -1,0 +1,208 @@
+"""The generation loop above the step function.
+
+Per request the reference resets, reserves `prompt + max_new`, prefills, decodes and
+resets again, on every exit path (crates/engine/src/model_engine/generation.rs:33-56,
+60-116).  The token chosen after the prompt counts toward the limit (:97-101); a stop token
+is neither returned nor fed back (:280-285); a request ends with `length` iff it produced
+`max_new` tokens, else `stop` (crates/engine/src/model_engine.rs:243-247); `max_new == 0`
+returns at once without touching the model (:152-159); an empty prompt is an error
+(:187-192); `prompt + max_new` must fit the context (crates/engine/src/model_engine/
+kv_budget.rs:126-134).  Here the unit is a batch: requests that start together with
+unequal prompts, prefilled in one packed step (or in chunks of it), decoded one token each
+per step; a request that ends gives its slot back at once and the rest go on; when there
+are more requests than fit, batches run one after another on the same cache.
+
+The loop needs only `open_sequence`, `close_sequence`, `step` and the two limits of a
+backend, and a `select` function, so its decisions can be tested with fakes.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..cache.sequence_cache import PAGE_TOKENS, pages_for
+from .batch import StepEntry
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str        # "stop" or "length"
+    prompt_tokens: int
+
+
+@dataclass
+class GenerationMetrics:
+    """Counters in the reference's sense (crates/metrics/src/serving.rs:35-54,84-93): the decode
+    rate is decoded tokens over the summed time of decode steps; the token that prefill produces
+    and stop tokens are not decoded tokens."""
+
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    decode_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    prefill_steps: int = 0
+    decode_steps: int = 0
+    batches: int = 0
+
+    @property
+    def decode_tokens_per_second(self) -> float:
+        return self.decode_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+    @property
+    def prefill_tokens_per_second(self) -> float:
+        return self.prompt_tokens / (self.prefill_ms / 1e3) if self.prefill_ms > 0 else 0.0
+
+    def as_dict(self) -> dict:
+        return {
+            "prompt_tokens": self.prompt_tokens, "generated_tokens": self.generated_tokens,
+            "decode_tokens": self.decode_tokens, "prefill_ms": round(self.prefill_ms, 3),
+            "decode_ms": round(self.decode_ms, 3),
+            "decode_tokens_per_second": round(self.decode_tokens_per_second, 2),
+            "prefill_tokens_per_second": round(self.prefill_tokens_per_second, 2),
+            "prefill_steps": self.prefill_steps, "decode_steps": self.decode_steps, "batches": self.batches,
+        }
+
+
+def plan_batches(needs: Sequence[int], max_batch: int, capacity_tokens: int) -> List[List[int]]:
+    """Splits request numbers `0..n` into consecutive batches.
+
+    `needs[i]` is the most tokens request `i` can come to hold.  A batch has at most
+    `max_batch` requests and its needs, each rounded up to whole pages, fit the cache.
+    """
+    batches: List[List[int]] = []
+    current: List[int] = []
+    used = 0
+    for index, need in enumerate(needs):
+        rounded = pages_for(need) * PAGE_TOKENS
+        if rounded > capacity_tokens:
+            raise ValueError(f"request {index} needs {rounded} cache tokens, the cache holds {capacity_tokens}")
+        if current and (len(current) >= max_batch or used + rounded > capacity_tokens):
+            batches.append(current)
+            current, used = [], 0
+        current.append(index)
+        used += rounded
+    if current:
+        batches.append(current)
+    return batches
+
+
+@dataclass
+class _Live:
+    request: int
+    slot: int
+    prompt: Sequence[int]
+    limit: int
+    fed: int = 0
+    produced: List[int] = field(default_factory=list)
+
+
+def generate_tokens(backend, prompts: Sequence[Sequence[int]], max_new_tokens, select: Callable, stop_tokens=(),
+                    max_batch: int = 64, prefill_chunk_tokens: Optional[int] = None,
+                    metrics: Optional[GenerationMetrics] = None) -> List[GenerationResult]:
+    """Generates for every prompt; results keep the order of the prompts.
+
+    `max_new_tokens` is one limit or one per prompt.  `select(logits, request_ids,
+    token_indices) -> tokens` chooses one token per logits row.  `backend` offers
+    `open_sequence()`, `close_sequence(slot)`, `step(entries)`, `capacity_tokens` and
+    `max_sequence_tokens`.
+    """
+    limits = list(max_new_tokens) if isinstance(max_new_tokens, (list, tuple)) else [max_new_tokens] * len(prompts)
+    if len(limits) != len(prompts):
+        raise ValueError("one output limit per prompt is needed")
+    if prefill_chunk_tokens is not None and prefill_chunk_tokens <= 0:
+        raise ValueError("prefill chunk size must be positive")
+    if max_batch <= 0:
+        raise ValueError("the batch size must be positive")
+    stop = frozenset(stop_tokens)
+    metrics = metrics if metrics is not None else GenerationMetrics()
+    for index, (prompt, limit) in enumerate(zip(prompts, limits)):
+        if limit < 0:
+            raise ValueError(f"request {index}: the output limit must not be negative")
+        if limit > 0 and len(prompt) == 0:
+            raise ValueError(f"request {index}: the prompt is empty")
+        if limit > 0 and len(prompt) + limit > backend.max_sequence_tokens:
+            raise ValueError(
+                f"request {index}: prompt ({len(prompt)}) plus output limit ({limit}) exceeds the "
+                f"context of {backend.max_sequence_tokens} tokens"
+            )
+    results: List[Optional[GenerationResult]] = [None] * len(prompts)
+    active = []
+    for index, (prompt, limit) in enumerate(zip(prompts, limits)):
+        if limit == 0:
+            results[index] = GenerationResult([], "length", len(prompt))
+        else:
+            active.append(index)
+    needs = [len(prompts[index]) + limits[index] for index in active]
+    for batch in plan_batches(needs, max_batch, backend.capacity_tokens):
+        metrics.batches += 1
+        _run_batch(backend, [active[position] for position in batch], prompts, limits, select, stop,
+                   prefill_chunk_tokens, metrics, results)
+    return results
+
+
+def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics, results) -> None:
+    live: List[_Live] = []
+    try:
+        for request in requests:
+            live.append(_Live(request, backend.open_sequence(), prompts[request], limits[request]))
+
+        def finish(item: _Live, reason: str) -> None:
+            results[item.request] = GenerationResult(item.produced, reason, len(item.prompt))
+            backend.close_sequence(item.slot)
+            live.remove(item)
+
+        def accept(item: _Live, token: int) -> None:
+            if token in stop:
+                finish(item, "stop")
+                return
+            item.produced.append(token)
+            metrics.generated_tokens += 1
+            if len(item.produced) == item.limit:
+                finish(item, "length")
+
+        # Prefill: the prompts packed along one axis, in chunks of at most `chunk` tokens.
+        first_tokens = {}
+        started = time.perf_counter()
+        while any(item.fed < len(item.prompt) for item in live):
+            budget = chunk if chunk is not None else sum(len(item.prompt) for item in live)
+            entries, owners = [], []
+            for item in live:
+                remaining = len(item.prompt) - item.fed
+                if remaining == 0 or budget == 0:
+                    continue
+                count = min(remaining, budget)
+                ends = item.fed + count == len(item.prompt)
+                entries.append(StepEntry(item.slot, item.prompt[item.fed : item.fed + count], [count - 1] if ends else []))
+                if ends:
+                    owners.append(item)
+                item.fed += count
+                budget -= count
+            logits = backend.step(entries)
+            metrics.prefill_steps += 1
+            if owners:
+                tokens = select(logits, [item.request for item in owners], [0] * len(owners))
+                for item, token in zip(owners, tokens):
+                    first_tokens[item.request] = token
+        metrics.prefill_ms += (time.perf_counter() - started) * 1e3
+        metrics.prompt_tokens += sum(len(item.prompt) for item in live)
+        for item in list(live):
+            accept(item, first_tokens[item.request])
+
+        # Decode: one token for every request that is still going.
+        while live:
+            started = time.perf_counter()
+            entries = [StepEntry(item.slot, [item.produced[-1]], [0]) for item in live]
+            logits = backend.step(entries)
+            tokens = select(logits, [item.request for item in live], [len(item.produced) for item in live])
+            metrics.decode_ms += (time.perf_counter() - started) * 1e3
+            metrics.decode_steps += 1
+            for item, token in zip(list(live), tokens):
+                if token not in stop:
+                    metrics.decode_tokens += 1
+                accept(item, token)
+    finally:
+        for item in list(live):
+            backend.close_sequence(item.slot)

@@ -1,0 +1,138 @@
+"""The step function: a batch of sequences, each with its next tokens, through the model once.
+
+The reference's contract per request is `forward(input [1, T], offset) -> logits` with
+`offset == cache length` (crates/models/src/interface.rs:24-28; crates/models/src/
+components/gated_attention/kv_cache.rs:85-111), a prompt first and then one token per call
+(crates/engine/src/model_engine/generation.rs:120-161,165-219).  Here one call takes
+many sequences with runs of unequal length: a first step carries whole prompts packed
+along one token axis, later steps carry one token each (or any mixture; a run continues
+where the sequence's cache ends).  Only the tokens given are computed, everything
+earlier is read from the cache, and logits come back only for the places asked for.
+Every check happens before anything is changed, so a refused step leaves the cache as it was.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.allocator import CacheFull
+from ..cache.sequence_cache import PAGE_TOKENS, SequenceCache, pages_for
+from .batch import StepContext, StepEntry, StepLayout, fill_step, step_views
+from .staging import PinnedRing
+
+
+class StepError(ValueError):
+    """The step's entries do not fit the sequences they name."""
+
+
+class Engine:
+    """A model, its cache and the step function over both."""
+
+    def __init__(self, model, max_tokens: int, max_sequence_tokens: Optional[int] = None, max_slots: Optional[int] = None):
+        self.model = model
+        self.device = torch.device(model.device)
+        limit = model.spec.max_positions
+        if max_sequence_tokens is not None:
+            limit = min(limit, max_sequence_tokens)
+        self.cache = SequenceCache(model.cache_groups(), max_tokens, limit, model.dtype, self.device, max_slots)
+        self._ring: Optional[PinnedRing] = None
+        self._graphs: Dict = {}
+        # A captured step runs more than once while it is captured; state that a mixer updates in place forbids that.
+        self.use_graphs = self.device.type == "cuda" and not self.cache.states
+
+    # ---- sequences ---------------------------------------------------------------
+    def open_sequence(self) -> int:
+        return self.cache.open()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def sequence_length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    @property
+    def capacity_tokens(self) -> int:
+        """Tokens the whole cache holds (whole pages)."""
+        return self.cache.n_pages * PAGE_TOKENS
+
+    @property
+    def max_sequence_tokens(self) -> int:
+        return self.cache.max_sequence_tokens
+
+    # ---- the step ----------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> List[int]:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        starts = []
+        pages_wanted = 0
+        vocab = self.model.spec.vocab_size
+        for entry in entries:
+            if entry.slot in seen:
+                raise StepError(f"sequence slot {entry.slot} appears twice in one step")
+            seen.add(entry.slot)
+            try:
+                start = self.cache.length(entry.slot)
+            except ValueError as error:
+                raise StepError(str(error)) from None
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepError(f"sequence slot {entry.slot} brings no token")
+            low, high = min(entry.tokens), max(entry.tokens)
+            if low < 0 or high >= vocab:
+                raise StepError(f"token id {low if low < 0 else high} lies outside the vocabulary of {vocab}")
+            for place in entry.want:
+                if not 0 <= place < count:
+                    raise StepError(f"wanted place {place} lies outside the {count} tokens of the step")
+            if start + count > self.cache.max_sequence_tokens:
+                raise CacheFull(
+                    f"sequence slot {entry.slot} would reach {start + count} tokens; the limit is {self.cache.max_sequence_tokens}"
+                )
+            pages_wanted += self.cache.pages_needed(entry.slot, start + count)
+            starts.append(start)
+        if pages_wanted * PAGE_TOKENS > self.cache.free_tokens():
+            raise CacheFull(
+                f"the step needs {pages_wanted} more cache pages of {PAGE_TOKENS} tokens, "
+                f"{self.cache.free_tokens() // PAGE_TOKENS} are free"
+            )
+        return starts
+
+    def _context(self, entries: Sequence[StepEntry], starts: Sequence[int], page_stride: Optional[int] = None,
+                 buffer: Optional[torch.Tensor] = None) -> StepContext:
+        n_tokens = sum(len(entry.tokens) for entry in entries)
+        n_wanted = sum(len(entry.want) for entry in entries)
+        max_new = max(len(entry.tokens) for entry in entries)
+        max_len = max(start + len(entry.tokens) for entry, start in zip(entries, starts))
+        stride = page_stride if page_stride is not None else pages_for(max_len)
+        layout = StepLayout(n_tokens, len(entries), n_wanted, {group: stride for group in self.cache.kv})
+        if buffer is None:
+            buffer = torch.empty(layout.total, dtype=torch.int32, device=self.device)
+        if self.device.type == "cuda":
+            if self._ring is None or self._ring.capacity < layout.total:
+                self._ring = PinnedRing(max(layout.total * 2, 1 << 16))
+            staged, ticket = self._ring.acquire(layout.total)
+            fill_step(layout, staged, entries, starts, self.cache)
+            self._ring.upload(ticket, layout.total, buffer)
+        else:
+            staged = np.zeros(layout.total, dtype=np.int32)
+            fill_step(layout, staged, entries, starts, self.cache)
+            buffer.copy_(torch.from_numpy(staged))
+        return step_views(layout, buffer, max_new, max_len, all(len(entry.tokens) == 1 for entry in entries))
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens; returns 32-bit logits `[wanted places, vocab]` in the order of the
+        entries and of their `want`, or None if nothing is wanted."""
+        starts = self._validate(entries)
+        for entry, start in zip(entries, starts):
+            self.cache.reserve(entry.slot, start + len(entry.tokens))
+        single = all(len(entry.tokens) == 1 and tuple(entry.want) == (0,) for entry in entries)
+        if single and self.use_graphs:
+            from .graph import run_decode_graph
+            logits = run_decode_graph(self, entries, starts)
+        else:
+            logits = self.model.forward(self._context(entries, starts), self.cache)
+        for entry, start in zip(entries, starts):
+            self.cache.advance(entry.slot, start + len(entry.tokens))
+        return logits

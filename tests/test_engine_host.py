@@ -1,0 +1,95 @@
+"""The engine's host logic on the CPU, with the kernels replaced by their plain torch statements.
+
+What is tested here is packing, page and slot bookkeeping, the schedule and the cache
+addressing, in every way of cutting the work; the CUDA kernels themselves are tested on the
+GPU.  Expected logits come from the plain whole-sequence implementation.
+"""
+import numpy as np
+import pytest
+import torch
+
+import plain_kernels
+import tiny_configs
+from helpers import (engine_for, plain_logits, random_prompts, relative_error, run_batched, run_tail_stepwise, run_whole)
+from tau_rs_b200 import CacheFull, Engine, StepEntry, StepError, load_model
+
+
+@pytest.fixture
+def cpu_kernels(monkeypatch):
+    plain_kernels.install(monkeypatch)
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {which: tiny_configs.write_tiny(str(root), which) for which in ("A", "B", "C")}
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_whole_prompt_matches_plain(cpu_kernels, folders, which):
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    engine = engine_for(folders[which], "float32", "cpu")
+    for tokens in random_prompts(vocab, [1, 17, 70], seed=5):
+        assert relative_error(run_whole(engine, tokens), plain_logits(folders[which], tokens)) < 1e-4
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_tail_stepwise_matches_whole(cpu_kernels, folders, which):
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    engine = engine_for(folders[which], "float32", "cpu")
+    (tokens,) = random_prompts(vocab, [100], seed=6)
+    wanted = plain_logits(folders[which], tokens)[-32:]
+    assert relative_error(run_tail_stepwise(engine, tokens, 32), wanted) < 1e-4
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_unequal_batches_reuse_slots(cpu_kernels, folders, which):
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    engine = engine_for(folders[which], "float32", "cpu", max_tokens=64 * 6)
+    lengths = [[5, 11, 17], [70, 3, 64, 1], [9, 65]]
+    steps = [8, 3, 16]
+    for wave, (prompt_lengths, extra) in enumerate(zip(lengths, steps)):
+        totals = [length + (extra if index % 2 == 0 else extra // 2) for index, length in enumerate(prompt_lengths)]
+        requests = random_prompts(vocab, totals, seed=10 + wave)
+        found = run_batched(engine, requests, prompt_lengths)
+        for request, prompt_length, logits in zip(requests, prompt_lengths, found):
+            wanted = plain_logits(folders[which], request)[prompt_length - 1 :]
+            assert logits.shape == wanted.shape
+            assert relative_error(logits, wanted) < 1e-4
+        engine.cache.check()
+        assert engine.cache.slots.in_use == 0
+
+
+def test_bfloat16_rounding_points_match_plain(cpu_kernels, folders):
+    engine = engine_for(folders["A"], "bfloat16", "cpu")
+    (tokens,) = random_prompts(256, [40], seed=3)
+    wanted = plain_logits(folders["A"], tokens, bf16=True)
+    assert relative_error(run_whole(engine, tokens), wanted) < 2e-2
+
+
+def test_step_refuses_bad_entries(cpu_kernels, folders):
+    engine = engine_for(folders["A"], "float32", "cpu", max_tokens=128)
+    slot = engine.open_sequence()
+    with pytest.raises(StepError):
+        engine.step([])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(slot, [], [])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(slot, [1, 2], [2])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(slot, [256], [0])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(slot, [1], [0]), StepEntry(slot, [2], [0])])
+    with pytest.raises(StepError):
+        engine.step([StepEntry(slot + 1, [1], [0])])
+    with pytest.raises(CacheFull):
+        engine.step([StepEntry(slot, list(range(129)), [0])])   # beyond max_position_embeddings
+    other = engine.open_sequence()
+    with pytest.raises(CacheFull):
+        engine.step([StepEntry(slot, list(range(100)), [0]), StepEntry(other, list(range(60)), [0])])  # 3 pages wanted, 2 exist
+    assert engine.sequence_length(slot) == 0 and engine.sequence_length(other) == 0
+    engine.cache.check()
+    assert engine.cache.free_tokens() == 128
+    assert engine.step([StepEntry(slot, [1, 2, 3], [])]) is None
+    assert engine.sequence_length(slot) == 3
