@@ -43,12 +43,18 @@ def resolve_dtype(requested: str, declared: Optional[str]) -> str:
     return canonical_dtype(requested)
 
 
-def load_model(folder: str, dtype: str = "auto", device="gpu") -> DecoderModel:
-    """Builds the model that the folder's config.json names and reads its weights."""
+def load_model(folder: str, dtype: str = "auto", device="gpu", enforce_declared_dtype: bool = True) -> DecoderModel:
+    """Builds the model that the folder's config.json names and reads its weights.
+
+    With `enforce_declared_dtype` a bfloat16 run needs a folder that declares bfloat16, as
+    the reference demands; without it any folder runs in either dtype.
+    """
     raw = read_config_json(folder)
     metadata = metadata_from_json(raw)
     entry = architecture_for(raw)
-    run_dtype = validate_run_dtype(metadata, resolve_dtype(dtype, metadata.declared_dtype))
+    run_dtype = resolve_dtype(dtype, metadata.declared_dtype)
+    if enforce_declared_dtype:
+        run_dtype = validate_run_dtype(metadata, run_dtype)
     spec = entry.build_spec(entry.parse_config(raw))
     target = device if isinstance(device, torch.device) else resolve_device(device)
     model = DecoderModel(spec, _TORCH_DTYPE[run_dtype], target)
@@ -72,9 +78,9 @@ def random_model(config_json: dict, seed: int = 0, dtype: str = "bfloat16", devi
 
 
 def load_engine(folder: str, dtype: str = "auto", device="gpu", max_tokens: int = 8192,
-                max_sequence_tokens: Optional[int] = None) -> Engine:
+                max_sequence_tokens: Optional[int] = None, enforce_declared_dtype: bool = True) -> Engine:
     """`max_tokens`: the most tokens that live sequences hold together (each rounded up to 64); it sizes the cache."""
-    return Engine(load_model(folder, dtype, device), max_tokens, max_sequence_tokens)
+    return Engine(load_model(folder, dtype, device, enforce_declared_dtype), max_tokens, max_sequence_tokens)
 
 
 @dataclass

@@ -1,1 +1,2 @@
 """Hand-written CUDA for sm_100a and its Python face (`kernels`)."""
+from . import build, libraries  # noqa: F401

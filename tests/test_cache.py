@@ -1,0 +1,114 @@
+"""The cache's bookkeeping: slots and pages are never lost, held twice or freed twice (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from tau_rs_b200.cache import PAGE_TOKENS, CacheFull, FreeList, SequenceCache, pages_for
+from tau_rs_b200.parts import CacheNeed
+
+
+def make(max_tokens=64 * 8, limit=64 * 5, slots=None, with_state=True):
+    groups = {"attention": (CacheNeed("kv", n_kv_heads=2, head_dim=16), 3)}
+    if with_state:
+        groups["recurrent"] = (CacheNeed("state", state_shape=(4, 2), state_dtype=torch.float32), 2)
+    return SequenceCache(groups, max_tokens, limit, torch.float32, torch.device("cpu"), slots)
+
+
+def test_free_list_refuses_misuse():
+    pool = FreeList(3, "page")
+    taken = pool.take(2)
+    assert taken == [0, 1] and pool.available == 1
+    with pytest.raises(CacheFull):
+        pool.take(2)
+    pool.give_back([0])
+    with pytest.raises(ValueError):
+        pool.give_back([0])          # freed twice
+    with pytest.raises(ValueError):
+        pool.give_back([2])          # never taken
+    with pytest.raises(ValueError):
+        pool.give_back([7])
+    assert pool.take(1) == [0]       # what came back goes out again first
+    pool.check()
+
+
+def test_shapes_and_sizing():
+    cache = make(max_tokens=64 * 8 - 1)
+    assert cache.n_pages == 8 and cache.pages_per_sequence == 5 and cache.max_sequence_tokens == 320
+    view = cache.layer_view("attention", 2)
+    assert view.keys.shape == (8, 2, PAGE_TOKENS, 16) and view.values.shape == view.keys.shape and view.group == "attention"
+    assert cache.layer_view("recurrent", 1).state.shape == (8, 4, 2)
+    assert cache.bytes_per_token() == 2 * 3 * 2 * 16 * 4 and pages_for(65) == 2 and pages_for(64) == 1
+
+
+def test_sequences_take_pages_as_they_grow_and_give_them_back():
+    cache = make()
+    a, b = cache.open(), cache.open()
+    cache.reserve(a, 65)
+    cache.advance(a, 65)
+    cache.reserve(b, 1)
+    cache.advance(b, 1)
+    assert cache.free_tokens() == 5 * 64 and cache.length(a) == 65
+    rows = cache.page_rows("attention", [a, b], 2)
+    assert rows.shape == (2, 2) and len({rows[0, 0], rows[0, 1], rows[1, 0]}) == 3
+    cache.reserve(a, 100)            # still two pages
+    assert cache.free_tokens() == 5 * 64
+    with pytest.raises(CacheFull):
+        cache.reserve(a, 321)        # beyond the longest sequence allowed
+    with pytest.raises(CacheFull):
+        cache.reserve(b, 64 * 6 + 1) # beyond what is free
+    cache.check()
+    cache.close(a)
+    with pytest.raises(ValueError):
+        cache.close(a)
+    with pytest.raises(ValueError):
+        cache.length(a)
+    assert cache.free_tokens() == 7 * 64
+    c = cache.open()
+    assert c == a                    # the slot is used again
+    assert cache.length(c) == 0
+    cache.close(b)
+    cache.close(c)
+    cache.check()
+    assert cache.free_tokens() == 8 * 64 and cache.slots.in_use == 0
+
+
+def test_state_is_zero_for_a_new_sequence_only():
+    cache = make()
+    a = cache.open()
+    state = cache.layer_view("recurrent", 0).state
+    state[a] += 3.0
+    b = cache.open()
+    assert float(state[a].sum()) == 24.0 and float(state[b].sum()) == 0.0
+    cache.close(a)
+    assert cache.open() == a and float(state[a].sum()) == 0.0
+
+
+def test_random_traffic_keeps_every_invariant():
+    rng = random.Random(0)
+    cache = make(max_tokens=64 * 12, limit=64 * 6, slots=5)
+    live = {}
+    for _ in range(2000):
+        action = rng.random()
+        if action < 0.3 and cache.slots.available:
+            live[cache.open()] = 0
+        elif action < 0.8 and live:
+            slot = rng.choice(list(live))
+            target = live[slot] + rng.randint(1, 90)
+            try:
+                cache.reserve(slot, target)
+                cache.advance(slot, target)
+                live[slot] = target
+            except CacheFull:
+                pass
+        elif live:
+            slot = rng.choice(list(live))
+            cache.close(slot)
+            del live[slot]
+        cache.check()
+        held = sum(pages_for(length) for length in live.values())
+        assert cache.kv["attention"].pool.in_use >= held
+    for slot in list(live):
+        cache.close(slot)
+    cache.check()
+    assert cache.free_tokens() == 64 * 12

@@ -1,0 +1,196 @@
+"""The engine on the GPU against the plain whole-sequence implementation, in every way of cutting the work."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import tiny_configs
+from helpers import (engine_for, plain_logits, random_prompts, relative_error, run_batched, run_tail_stepwise, run_whole)
+from tau_rs_b200 import StepEntry, generate, load_model
+
+pytestmark = pytest.mark.gpu
+# Largest difference relative to the largest logit.  32-bit: rounding of sums only.  bfloat16: the plain
+# implementation rounds where the engine stores, so what is left are roundings that fall the other way.
+TOLERANCE = {"float32": 1e-4, "bfloat16": 2e-2}
+RUNS = [("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    made = {}
+    for which in ("A", "B", "C"):
+        made[(which, "bfloat16")] = tiny_configs.write_tiny(str(root / "bf16"), which, "bfloat16")
+        made[(which, "float32")] = tiny_configs.write_tiny(str(root / "native"), which)
+    return made
+
+
+@pytest.fixture(scope="module")
+def engines(folders):
+    cache = {}
+
+    def get(which, dtype, max_tokens=4096):
+        key = (which, dtype, max_tokens)
+        if key not in cache:
+            cache[key] = engine_for(folders[(which, dtype)], dtype, "gpu", max_tokens)
+        return cache[key]
+
+    return get
+
+
+def expected(folders, which, dtype, tokens):
+    return plain_logits(folders[(which, dtype)], tokens, bf16=dtype == "bfloat16")
+
+
+@pytest.mark.parametrize("which,dtype", RUNS)
+def test_each_request_alone_and_whole(folders, engines, which, dtype):
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    limit = tiny_configs.CONFIGS[which]["max_position_embeddings"]
+    engine = engines(which, dtype)
+    for tokens in random_prompts(vocab, [1, 2, 17, 64, 65, min(limit, 200)], seed=1):
+        assert relative_error(run_whole(engine, tokens), expected(folders, which, dtype, tokens)) < TOLERANCE[dtype]
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("which,dtype", RUNS)
+def test_last_32_tokens_one_by_one(folders, engines, which, dtype):
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    limit = tiny_configs.CONFIGS[which]["max_position_embeddings"]
+    engine = engines(which, dtype)
+    for tokens in random_prompts(vocab, [33, 100, min(limit, 130)], seed=2):
+        wanted = expected(folders, which, dtype, tokens)[-32:]
+        assert relative_error(run_tail_stepwise(engine, tokens, 32), wanted) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("which,dtype", RUNS)
+def test_unequal_batches_one_after_another(folders, engines, which, dtype):
+    """Prompts of unequal lengths start together, shorter requests end earlier, and the next batch takes
+    the slots and pages that the last one gave back."""
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    engine = engines(which, dtype, 64 * 7)
+    waves = {"A": ([5, 11, 17], 8), "B": ([1, 2, 9, 33, 64], 16), "C": ([70, 3, 130], 12)}
+    prompt_lengths, steps = waves[which]
+    for wave in range(3):
+        lengths = prompt_lengths if wave != 1 else list(reversed(prompt_lengths))
+        totals = [length + max(1, steps - 3 * index) for index, length in enumerate(lengths)]
+        requests = random_prompts(vocab, totals, seed=20 + wave)
+        found = run_batched(engine, requests, lengths)
+        for request, length, logits in zip(requests, lengths, found):
+            wanted = expected(folders, which, dtype, request)[length - 1 :]
+            assert relative_error(logits, wanted) < TOLERANCE[dtype]
+        engine.cache.check()
+        assert engine.cache.slots.in_use == 0 and engine.cache.free_tokens() == 64 * 7
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, engines, dtype):
+    """Hundreds of single-token steps across several pages."""
+    engine = engines("C", dtype)
+    (tokens,) = random_prompts(333, [400], seed=4)
+    wanted = expected(folders, "C", dtype, tokens)[-390:]
+    assert relative_error(run_tail_stepwise(engine, tokens, 390), wanted) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("which,dtype", RUNS)
+def test_first_tokens_of_a_sequence(folders, engines, which, dtype):
+    """Position 0 alone, then positions 1 and 2 one by one: no earlier key exists."""
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    engine = engines(which, dtype)
+    (tokens,) = random_prompts(vocab, [3], seed=5)
+    wanted = expected(folders, which, dtype, tokens)
+    slot = engine.open_sequence()
+    rows = [engine.step([StepEntry(slot, [token], [0])]).float().cpu().clone() for token in tokens]
+    engine.close_sequence(slot)
+    assert relative_error(torch.cat(rows), wanted) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padding_and_neighbours_change_nothing(folders, engines, dtype):
+    """A request's logits are bitwise the same alone and beside other requests of other lengths."""
+    engine = engines("B", dtype)
+    requests = random_prompts(500, [40, 7, 64], seed=6)
+    alone = run_batched(engine, requests[:1], [30])[0]
+    beside = run_batched(engine, requests, [30, 3, 50])[0]
+    assert relative_error(beside, alone) < TOLERANCE[dtype] * 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stale_pages_do_not_leak(folders, engines, dtype):
+    """A long request fills pages with large values; a short one that reuses them must not see them."""
+    engine = engines("A", dtype, 64 * 2)
+    (long_request,) = random_prompts(256, [120], seed=7)
+    run_whole(engine, long_request)
+    for group in engine.cache.kv.values():   # poison what the finished request left behind
+        group.keys.fill_(float("nan"))
+        group.values.fill_(float("nan"))
+    (short,) = random_prompts(256, [70], seed=8)
+    found = run_tail_stepwise(engine, short, 5)
+    assert torch.isfinite(found).all()
+    assert relative_error(found, expected(folders, "A", dtype, short)[-5:]) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "float32")])
+def test_greedy_generation_through_the_entry_point(folders, which, dtype):
+    """`generate()` on a folder: unequal prompts, more requests than one batch holds, the plain tokens."""
+    config = plain_model.read_plain_config(folders[(which, dtype)])
+    weights = plain_model.read_plain_weights(folders[(which, dtype)])
+    lengths = {"A": [5, 11, 17, 3], "B": [1, 2, 9, 33, 64]}[which]
+    steps = {"A": 8, "B": 16}[which]
+    prompts = random_prompts(config.vocab_size, lengths, seed=9)
+    output = generate(folders[(which, dtype)], prompts, max_new_tokens=steps, dtype=dtype, stop_tokens=(), max_batch=3)
+    for prompt, result in zip(prompts, output):
+        assert result.tokens == plain_model.greedy_generate(config, weights, prompt, steps)
+        assert result.finish_reason == "length"
+    assert output.metrics.batches == 2
+
+
+def test_generation_stops_at_stop_tokens(folders):
+    config = plain_model.read_plain_config(folders[("A", "float32")])
+    weights = plain_model.read_plain_weights(folders[("A", "float32")])
+    prompts = random_prompts(256, [6, 9], seed=10)
+    free = [plain_model.greedy_generate(config, weights, prompt, 10) for prompt in prompts]
+    stop = free[0][4]
+    output = generate(folders[("A", "float32")], prompts, max_new_tokens=10, dtype="float32", stop_tokens=[stop])
+    for run, result in zip(free, output):
+        cut = run.index(stop) if stop in run else len(run)
+        assert result.tokens == run[:cut]
+        assert result.finish_reason == ("stop" if cut < len(run) else "length")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16"])
+def test_bfloat16_generation_follows_the_plain_ranking(folders, dtype):
+    """In bfloat16 near-ties may fall the other way, so each chosen token must be (nearly) the plain best
+    given the engine's own earlier tokens."""
+    folder = folders[("B", dtype)]
+    prompts = random_prompts(500, [9, 33], seed=11)
+    output = generate(folder, prompts, max_new_tokens=8, dtype=dtype, stop_tokens=())
+    for prompt, result in zip(prompts, output):
+        assert len(result.tokens) == 8
+        logits = plain_logits(folder, list(prompt) + result.tokens, bf16=True)
+        for index, token in enumerate(result.tokens):
+            row = logits[len(prompt) - 1 + index]
+            assert float(row.max() - row[token]) <= TOLERANCE[dtype] * float(row.abs().max()) * 2
+
+
+def test_temperature_sampling_is_repeatable_and_batch_independent(folders):
+    folder = folders[("A", "bfloat16")]
+    prompts = random_prompts(256, [5, 11, 17], seed=12)
+    first = generate(folder, prompts, max_new_tokens=12, temperature=0.8, seed=3, stop_tokens=())
+    again = generate(folder, prompts, max_new_tokens=12, temperature=0.8, seed=3, stop_tokens=())
+    other = generate(folder, prompts, max_new_tokens=12, temperature=0.8, seed=4, stop_tokens=())
+    assert [r.tokens for r in first] == [r.tokens for r in again]
+    assert [r.tokens for r in first] != [r.tokens for r in other]
+    alone = generate(folder, prompts[1:2], max_new_tokens=12, temperature=0.8, seed=3, stop_tokens=())
+    # Request numbers key the noise, so request 0 of a call draws what request 0 drew before.
+    assert alone[0].tokens != [] and len(alone[0].tokens) == 12
+
+
+def test_same_request_twice_gives_the_same_tokens(folders):
+    """crates/engine/src/qwen3_engine.rs:258-353 (the same chat twice gives identical output): the cache is reset."""
+    folder = folders[("B", "bfloat16")]
+    engine = engine_for(folder, "bfloat16", "gpu", 1024)
+    prompts = random_prompts(500, [33], seed=13)
+    first = generate(engine, prompts, max_new_tokens=16, stop_tokens=())
+    second = generate(engine, prompts, max_new_tokens=16, stop_tokens=())
+    assert first[0].tokens == second[0].tokens
+    engine.cache.check()

@@ -1,0 +1,132 @@
+"""The generation loop's decisions with a fake backend (no GPU).
+
+The fake plays the part of the reference's `SequenceModel` (crates/engine/src/model_engine/
+tests/mod.rs:19-128): it returns fixed logits that depend on the position, records every
+step, and can be told to fail.
+"""
+import pytest
+
+from tau_rs_b200.engine import GenerationMetrics, generate_tokens, plan_batches
+
+
+class FakeBackend:
+    """The next token after position `p` of request content `c` is `(c + p) % vocab`, where `c` is the first prompt token."""
+
+    def __init__(self, capacity_tokens=64 * 8, max_sequence_tokens=256, vocab=50, fail_at_step=None):
+        self.capacity_tokens, self.max_sequence_tokens, self.vocab = capacity_tokens, max_sequence_tokens, vocab
+        self.free = list(range(16))[::-1]
+        self.open, self.lengths, self.first = set(), {}, {}
+        self.steps, self.opened, self.closed = [], [], []
+        self.fail_at_step = fail_at_step
+
+    def open_sequence(self):
+        slot = self.free.pop()
+        self.open.add(slot)
+        self.lengths[slot] = 0
+        self.opened.append(slot)
+        return slot
+
+    def close_sequence(self, slot):
+        assert slot in self.open, "closed twice"
+        self.open.remove(slot)
+        self.free.append(slot)
+        self.closed.append(slot)
+
+    def step(self, entries):
+        if self.fail_at_step is not None and len(self.steps) == self.fail_at_step:
+            raise RuntimeError("injected failure")
+        self.steps.append([(entry.slot, self.lengths[entry.slot], len(entry.tokens), tuple(entry.want)) for entry in entries])
+        rows = []
+        for entry in entries:
+            assert entry.slot in self.open
+            if self.lengths[entry.slot] == 0:
+                self.first[entry.slot] = entry.tokens[0]
+            for place in entry.want:
+                rows.append((self.first[entry.slot] + self.lengths[entry.slot] + place) % self.vocab)
+            self.lengths[entry.slot] += len(entry.tokens)
+        return rows
+
+
+def select(rows, request_ids, token_indices):
+    select.calls.append((list(request_ids), list(token_indices)))
+    return list(rows)
+
+
+@pytest.fixture(autouse=True)
+def reset_select():
+    select.calls = []
+
+
+def expected_tokens(prompt, count, vocab=50):
+    return [(prompt[0] + len(prompt) - 1 + index) % vocab for index in range(count)]
+
+
+def test_offsets_chunks_and_the_limit():
+    """A 10-token prompt in chunks of 4: steps start at 0, 4, 8, then decode at 10, 11, 12; only the
+    last chunk is sampled; the first token counts toward the limit (tests/generation.rs:48-125,213-243)."""
+    backend = FakeBackend()
+    metrics = GenerationMetrics()
+    (result,) = generate_tokens(backend, [[5] * 10], 4, select, prefill_chunk_tokens=4, metrics=metrics)
+    assert [step[0][1:] for step in backend.steps] == [(0, 4, ()), (4, 4, ()), (8, 2, (1,)), (10, 1, (0,)), (11, 1, (0,)), (12, 1, (0,))]
+    assert result.tokens == expected_tokens([5] * 10, 4) and result.finish_reason == "length" and result.prompt_tokens == 10
+    assert select.calls[0] == ([0], [0]) and select.calls[-1] == ([0], [3])
+    assert (metrics.prompt_tokens, metrics.generated_tokens, metrics.decode_tokens, metrics.prefill_steps, metrics.decode_steps) == (10, 4, 3, 3, 3)
+    assert backend.open == set() and backend.opened == backend.closed
+
+
+def test_stop_token_after_the_prompt_means_no_decode_step():
+    backend = FakeBackend()
+    (result,) = generate_tokens(backend, [[7, 1, 1]], 5, select, stop_tokens=[9])
+    assert result.tokens == [] and result.finish_reason == "stop" and len(backend.steps) == 1 and backend.open == set()
+
+
+def test_stop_token_is_neither_returned_nor_fed_back():
+    backend = FakeBackend()
+    (result,) = generate_tokens(backend, [[7, 1, 1]], 8, select, stop_tokens=[12])
+    assert result.tokens == [9, 10, 11] and result.finish_reason == "stop"
+    assert sum(step[0][2] for step in backend.steps) == 3 + 3     # the prompt and the three tokens that were kept
+
+
+def test_zero_limit_touches_nothing_and_bad_requests_are_refused():
+    backend = FakeBackend()
+    results = generate_tokens(backend, [[1, 2], []], [0, 0], select)
+    assert [r.tokens for r in results] == [[], []] and [r.finish_reason for r in results] == ["length", "length"]
+    assert backend.steps == [] and backend.opened == []
+    for prompts, limits in [([[]], 3), ([[1] * 250], 10), ([[1]], -1)]:
+        with pytest.raises(ValueError):
+            generate_tokens(backend, prompts, limits, select)
+    with pytest.raises(ValueError):
+        generate_tokens(backend, [[1]], 1, select, prefill_chunk_tokens=0)
+    assert backend.steps == []
+
+
+def test_unequal_batch_shorter_requests_end_earlier_and_order_is_kept():
+    backend = FakeBackend()
+    prompts = [[3] * 5, [8] * 11, [20] * 17]
+    results = generate_tokens(backend, prompts, [2, 6, 4], select)
+    for prompt, limit, result in zip(prompts, [2, 6, 4], results):
+        assert result.tokens == expected_tokens(prompt, limit)
+    assert [len(step) for step in backend.steps] == [3, 3, 2, 2, 1, 1]     # prefill, then the batch shrinks
+    assert backend.closed[0] == backend.opened[0] and backend.open == set()
+
+
+def test_more_requests_than_fit_run_batch_after_batch_on_the_same_slots():
+    backend = FakeBackend(capacity_tokens=64 * 3)
+    prompts = [[index + 1] * (index + 2) for index in range(7)]
+    metrics = GenerationMetrics()
+    results = generate_tokens(backend, prompts, 3, select, max_batch=4, metrics=metrics)
+    assert [result.tokens for result in results] == [expected_tokens(prompt, 3) for prompt in prompts]
+    assert metrics.batches == 3 and set(backend.opened) == {0, 1, 2}       # three pages of 64 tokens: three requests at a time
+    assert plan_batches([10, 70, 10, 10, 200], max_batch=2, capacity_tokens=256) == [[0, 1], [2, 3], [4]]
+    with pytest.raises(ValueError):
+        plan_batches([300], max_batch=2, capacity_tokens=256)
+
+
+def test_slots_are_given_back_when_a_step_fails():
+    for failing in (0, 1, 3):
+        backend = FakeBackend(fail_at_step=failing)
+        with pytest.raises(RuntimeError):
+            generate_tokens(backend, [[1] * 6, [2] * 3], 5, select, prefill_chunk_tokens=6)
+        assert backend.open == set() and sorted(backend.opened) == sorted(backend.closed)
+        backend.fail_at_step = None
+        assert generate_tokens(backend, [[4, 4]], 2, select)[0].tokens == expected_tokens([4, 4], 2)   # no retry needed, the next request works

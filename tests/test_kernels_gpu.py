@@ -1,0 +1,297 @@
+"""Each CUDA kernel alone against its plain statement, at sizes other than the engine's."""
+import numpy as np
+import pytest
+import torch
+
+import plain_kernels
+from tau_rs_b200.csrc import kernels
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+# Relative to the largest expected magnitude; bfloat16 stores keep 8 bits.
+TOLERANCE = {torch.float32: 2e-5, torch.bfloat16: 1e-2}
+
+
+def close(found, wanted, dtype, scale=1.0):
+    found, wanted = found.double().cpu(), wanted.double().cpu()
+    error = float((found - wanted).abs().max() / wanted.abs().max().clamp_min(1e-30))
+    assert error < TOLERANCE[dtype] * scale, error
+
+
+def randn(*shape, dtype, seed, scale=1.0):
+    generator = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=generator) * scale).to(dtype).to(DEVICE)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,vocab", [(7, 11), (96, 500), (1000, 333)])
+def test_embedding(dtype, width, vocab):
+    table = randn(vocab, width, dtype=dtype, seed=1)
+    tokens = torch.tensor([0, vocab - 1, 3, 3, vocab // 2], dtype=torch.int32, device=DEVICE)
+    out = torch.empty(5, width, dtype=dtype, device=DEVICE)
+    kernels.embedding(tokens, table, out)
+    assert torch.equal(out, table[tokens.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps", [(1, 16, 1e-6), (5, 97, 1e-5), (3, 1000, 1e-3), (2, 4100, 1e-6)])
+def test_rms_norm(dtype, rows, width, eps):
+    values = randn(rows, width, dtype=dtype, seed=2, scale=3.0)
+    branch = randn(rows, width, dtype=dtype, seed=3)
+    weight = (1 + 0.1 * torch.randn(width, generator=torch.Generator().manual_seed(4))).to(DEVICE)
+    for use_branch in (False, True):
+        for picked in (None, torch.tensor([rows - 1, 0, rows - 1], dtype=torch.int32, device=DEVICE)):
+            count = rows if picked is None else 3
+            found = torch.empty(count, width, dtype=dtype, device=DEVICE)
+            wanted = torch.empty(count, width, dtype=dtype)
+            before = values.clone()
+            kernels.rms_norm(values, weight, eps, found, picked, branch if use_branch else None)
+            plain_kernels.rms_norm(values.cpu(), weight.cpu(), eps, wanted, None if picked is None else picked.cpu(),
+                                   branch.cpu() if use_branch else None)
+            close(found, wanted, dtype)
+            assert torch.equal(values, before)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(1, 64), (4, 97), (3, 2050)])
+def test_add_rms_norm(dtype, rows, width):
+    branch = randn(rows, width, dtype=dtype, seed=5)
+    residual = randn(rows, width, dtype=dtype, seed=6, scale=2.0)
+    weight = (1 + 0.1 * torch.randn(width, generator=torch.Generator().manual_seed(7))).to(DEVICE)
+    wanted_residual, wanted = residual.cpu().clone(), torch.empty(rows, width, dtype=dtype)
+    plain_kernels.add_rms_norm(branch.cpu(), wanted_residual, weight.cpu(), 1e-6, wanted)
+    found = torch.empty_like(residual)
+    kernels.add_rms_norm(branch, residual, weight, 1e-6, found)
+    assert torch.equal(residual.cpu(), wanted_residual)   # one rounded sum, the same on both sides
+    close(found, wanted, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(1, 1), (3, 225), (70, 1000)])
+def test_silu_mul(dtype, rows, width):
+    stacked = randn(rows, 2 * width, dtype=dtype, seed=8, scale=4.0)
+    found = torch.empty(rows, width, dtype=dtype, device=DEVICE)
+    wanted = torch.empty(rows, width, dtype=dtype)
+    kernels.silu_mul(stacked, found)
+    plain_kernels.silu_mul(stacked.cpu(), wanted)
+    close(found, wanted, dtype)
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (3, 70, 33), (65, 130, 100), (128, 64, 256), (9, 500, 96)])
+def test_gemm_simt(dtype, out_dtype, m, n, k):
+    values = randn(m, k, dtype=dtype, seed=9)
+    weight = randn(n, k, dtype=dtype, seed=10)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(11)).to(DEVICE)
+    for use_bias in (None, bias):
+        found = torch.empty(m, n, dtype=out_dtype, device=DEVICE)
+        wanted = torch.empty(m, n, dtype=out_dtype)
+        kernels.gemm_simt(values, weight, use_bias, found)
+        plain_kernels.linear(values.cpu(), weight.cpu(), None if use_bias is None else use_bias.cpu(), wanted)
+        close(found, wanted, out_dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_dispatch_matches_plain(dtype):
+    """Whatever kernel `linear` picks for a shape, the product is the same: ragged and aligned shapes, views of a stack."""
+    for m, n, k in [(1, 64, 64), (8, 6144 // 8, 512), (17, 257, 136), (64, 96, 224), (200, 128, 128), (5, 500, 96)]:
+        values = randn(m, k, dtype=dtype, seed=12)
+        stack = randn(n + 16, k, dtype=dtype, seed=13)
+        weight = stack[:n]
+        bias = torch.randn(n, generator=torch.Generator().manual_seed(14)).to(DEVICE)
+        for out_dtype in {dtype, torch.float32}:
+            found = torch.empty(m, n, dtype=out_dtype, device=DEVICE)
+            wanted = torch.empty(m, n, dtype=out_dtype)
+            kernels.linear(values, weight, bias, found)
+            plain_kernels.linear(values.cpu(), weight.cpu(), bias.cpu(), wanted)
+            close(found, wanted, out_dtype)
+
+
+def paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed, pages=40):
+    """Random cache pages, page rows that scatter each sequence over the pool, and the step's metadata."""
+    rng = np.random.default_rng(seed)
+    keys = randn(pages, n_kv_heads, 64, head_dim, dtype=dtype, seed=seed + 1)
+    values = randn(pages, n_kv_heads, 64, head_dim, dtype=dtype, seed=seed + 2)
+    order = rng.permutation(pages)
+    stride = max((length + 63) // 64 for length in lengths)
+    rows = np.zeros((len(lengths), stride), dtype=np.int32)
+    cursor = 0
+    for index, length in enumerate(lengths):
+        count = (length + 63) // 64
+        rows[index, :count] = order[cursor : cursor + count]
+        cursor += count
+    positions, token_seq = [], []
+    for index, (length, new) in enumerate(zip(lengths, new_counts)):
+        positions += list(range(length - new, length))
+        token_seq += [index] * new
+    to_device = lambda array: torch.tensor(np.asarray(array), dtype=torch.int32, device=DEVICE)
+    return keys, values, to_device(rows), to_device(positions), to_device(token_seq)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,rotary_dim,with_norm", [
+    (4, 2, 16, 16, True), (6, 3, 48, 48, True), (8, 1, 32, 16, True), (3, 3, 128, 128, False), (2, 1, 256, 0, True)])
+def test_attention_prepare(dtype, n_heads, n_kv_heads, head_dim, rotary_dim, with_norm):
+    lengths, new_counts = [70, 5, 129], [70, 1, 3]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=20)
+    tokens = positions.shape[0]
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    projected = randn(tokens, width + 8, dtype=dtype, seed=21)[:, :width]   # a view with a wider row stride
+    generator = torch.Generator().manual_seed(22)
+    q_weight = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(DEVICE) if with_norm else None
+    k_weight = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(DEVICE) if with_norm else None
+    angles = torch.rand(200, max(rotary_dim // 2, 1), generator=generator) * 6.0
+    cos, sin = (torch.cos(angles).to(DEVICE), torch.sin(angles).to(DEVICE)) if rotary_dim else (None, None)
+    for write in (True, False):
+        found_q = torch.empty(tokens, n_heads * head_dim, dtype=dtype, device=DEVICE)
+        found_k, found_v = keys.clone(), values.clone()
+        kernels.attention_prepare(projected, found_q, found_k, found_v, write, q_weight, k_weight, 1e-5, cos, sin, rotary_dim,
+                                  positions, token_seq, rows, n_heads, n_kv_heads, head_dim)
+        cpu = lambda t: None if t is None else t.cpu()
+        wanted_q = torch.empty(tokens, n_heads * head_dim, dtype=dtype)
+        wanted_k, wanted_v = keys.cpu().clone(), values.cpu().clone()
+        plain_kernels.attention_prepare(projected.cpu(), wanted_q, wanted_k, wanted_v, write, cpu(q_weight), cpu(k_weight), 1e-5,
+                                        cpu(cos), cpu(sin), rotary_dim, positions.cpu(), token_seq.cpu(), rows.cpu(), n_heads,
+                                        n_kv_heads, head_dim)
+        close(found_q, wanted_q, dtype)
+        close(found_k, wanted_k, dtype)
+        assert torch.equal(found_v.cpu(), wanted_v)
+        untouched = (wanted_k == keys.cpu())
+        assert torch.equal(found_k.cpu()[untouched], keys.cpu()[untouched])   # nothing else in the pool is written
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (4, 2, 16, 0), (6, 3, 48, 0), (8, 1, 32, 0), (5, 5, 128, 0), (2, 1, 256, 0), (4, 2, 64, 37)])
+def test_attention_over_pages(dtype, n_heads, n_kv_heads, head_dim, window):
+    """Prompts, single tokens and continued runs in one launch, against the plain statement."""
+    lengths, new_counts = [70, 200, 129, 1, 64], [70, 1, 3, 1, 1]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=30)
+    tokens = positions.shape[0]
+    queries = randn(tokens, n_heads * head_dim, dtype=dtype, seed=31)
+    found = torch.empty_like(queries)
+    wanted = torch.empty(tokens, n_heads * head_dim, dtype=dtype)
+    scale = head_dim ** -0.5
+
+    class Step:
+        pass
+
+    step = Step()
+    step.positions, step.token_seq, step.n_tokens, step.n_seqs = positions, token_seq, tokens, len(lengths)
+    step.max_new, step.max_len, step.all_single, step.decode_splits = max(new_counts), max(lengths), False, 0
+    step.cu_seqlens = torch.tensor(np.concatenate([[0], np.cumsum(new_counts)]), dtype=torch.int32, device=DEVICE)
+    step.seq_start = torch.tensor([l - n for l, n in zip(lengths, new_counts)], dtype=torch.int32, device=DEVICE)
+    step.seq_len = torch.tensor(lengths, dtype=torch.int32, device=DEVICE)
+    kernels.attention(queries, keys, values, found, step, rows, n_heads, n_kv_heads, head_dim, scale, window)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, scale, window)
+    close(found, wanted, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim", [(4, 2, 16), (8, 2, 128), (6, 1, 80)])
+def test_decode_attention_finds_a_far_key(dtype, n_heads, n_kv_heads, head_dim):
+    """One token per sequence over long contexts; one far key is scaled so that its value must dominate."""
+    lengths = [1500, 63, 1025, 700]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, [1] * 4, n_kv_heads, head_dim, dtype, seed=40, pages=64)
+    queries = randn(4, n_heads * head_dim, dtype=dtype, seed=41)
+    far = [3, 0, 1000, 64]
+    for index, place in enumerate(far):
+        page = int(rows[index, place // 64])
+        for head in range(n_kv_heads):
+            query = queries[index].view(n_heads, head_dim)[head * (n_heads // n_kv_heads)].float()
+            keys[page, head, place % 64] = (query * 40.0 / query.norm()).to(dtype)
+    found = torch.empty_like(queries)
+    wanted = torch.empty(4, n_heads * head_dim, dtype=dtype)
+
+    class Step:
+        pass
+
+    step = Step()
+    step.positions, step.token_seq, step.n_tokens, step.n_seqs = positions, token_seq, 4, 4
+    step.max_new, step.max_len, step.all_single, step.decode_splits = 1, max(lengths), True, 0
+    step.cu_seqlens = torch.arange(5, dtype=torch.int32, device=DEVICE)
+    step.seq_start = torch.tensor([l - 1 for l in lengths], dtype=torch.int32, device=DEVICE)
+    step.seq_len = torch.tensor(lengths, dtype=torch.int32, device=DEVICE)
+    kernels.attention(queries, keys, values, found, step, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, 0)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, head_dim ** -0.5, 0)
+    close(found, wanted, dtype)
+    for index, place in enumerate(far):   # the first head of each group reproduces the far value
+        page = int(rows[index, place // 64])
+        got = found[index].view(n_heads, head_dim)[0].float()
+        assert torch.allclose(got, values[page, 0, place % 64].float(), atol=0.05, rtol=0.05)
+
+
+def adversarial_rows():
+    nan, inf = float("nan"), float("inf")
+    rows = [
+        [nan, nan, nan], [nan, -inf, nan], [1.0, 2.0, 2.0, 1.0], [2.0, 1.0, 2.0], [-0.0, 0.0, -0.0], [0.0, -0.0],
+        [inf, 3.0, inf], [-inf, -inf], [nan, 5.0, nan, 5.0, nan], [1e-45, 0.0, -1e-45], [-1.0, -2.0, -1.0],
+    ]
+    return rows
+
+
+def test_argmax_semantics():
+    """The reference's cases: NaN never wins, +-inf, signed zeros, subnormals, ties go to the highest id
+    (crates/engine/src/generation/greedy/tests.rs:18-48)."""
+    for row in adversarial_rows():
+        logits = torch.tensor([row], dtype=torch.float32, device=DEVICE)
+        tokens = torch.full((1,), -7, dtype=torch.int32, device=DEVICE)
+        valid = torch.full((1,), -7, dtype=torch.int32, device=DEVICE)
+        kernels.argmax(logits, tokens, valid)
+        token, ok = plain_kernels.argmax_row(np.asarray(row, dtype=np.float32))
+        assert int(valid[0]) == ok, row
+        if ok:
+            assert int(tokens[0]) == token, row
+
+
+@pytest.mark.parametrize("vocab", [1, 31, 32, 33, 255, 256, 257, 2047, 2048, 2049, 151936])
+def test_argmax_random_bit_patterns(vocab):
+    rng = np.random.default_rng(vocab)
+    bits = rng.integers(0, 2 ** 32, size=(5, vocab), dtype=np.uint64).astype(np.uint32)
+    bits[1, :] = bits[1, 0]                      # all equal: the last index wins
+    bits[2, :] = 0x7FC00000                      # all NaN
+    if vocab > 2:
+        bits[3, vocab // 2] = 0x7F800000         # one +inf
+        bits[3, -1] = 0x7F800000                 # ... and a later one
+    values = bits.view(np.float32)
+    logits = torch.from_numpy(values.copy()).to(DEVICE)
+    tokens = torch.empty(5, dtype=torch.int32, device=DEVICE)
+    valid = torch.empty(5, dtype=torch.int32, device=DEVICE)
+    kernels.argmax(logits, tokens, valid)
+    for row in range(5):
+        token, ok = plain_kernels.argmax_row(values[row])
+        assert int(valid[row]) == ok
+        if ok:
+            assert int(tokens[row]) == token
+
+
+def test_gumbel_sampling_matches_plain_and_distribution():
+    vocab, rows = 700, 6
+    logits = torch.randn(rows, vocab, generator=torch.Generator().manual_seed(50)) * 2.0
+    logits[2, 5] = float("nan")
+    device_logits = logits.to(DEVICE)
+    requests = torch.tensor([0, 1, 2, 3, 4, 4], dtype=torch.int32, device=DEVICE)
+    indices = torch.tensor([0, 0, 9, 1, 7, 8], dtype=torch.int32, device=DEVICE)
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEVICE)
+    valid = torch.empty(rows, dtype=torch.int32, device=DEVICE)
+    kernels.sample_gumbel(device_logits, tokens, valid, 1.0 / 0.8, 1234567890123, requests, indices)
+    for row in range(rows):
+        scores = plain_kernels.gumbel_scores(logits[row].numpy(), 1.0 / 0.8, 1234567890123, int(requests[row]), int(indices[row]))
+        best = np.nanmax(scores)
+        assert int(valid[row]) == 1
+        assert scores[int(tokens[row])] >= best - 1e-4 * max(1.0, abs(best))   # log differs in the last bits only
+    # The same request and token index give the same token whatever else is in the batch.
+    alone = torch.empty(1, dtype=torch.int32, device=DEVICE)
+    kernels.sample_gumbel(device_logits[4:5].contiguous(), alone, valid[:1].clone(), 1.0 / 0.8, 1234567890123, requests[4:5], indices[4:5])
+    assert int(alone[0]) == int(tokens[4])
+    # Frequencies follow softmax(logits / T).
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, float("-inf")]], device=DEVICE).repeat(4000, 1).contiguous()
+    draws = torch.empty(4000, dtype=torch.int32, device=DEVICE)
+    kernels.sample_gumbel(small, draws, torch.empty(4000, dtype=torch.int32, device=DEVICE), 1.0 / 0.5, 7,
+                          torch.arange(4000, dtype=torch.int32, device=DEVICE), torch.zeros(4000, dtype=torch.int32, device=DEVICE))
+    counts = torch.bincount(draws.long().cpu(), minlength=5).double() / 4000
+    expected = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0, float("-inf")]).double() / 0.5, dim=0)
+    assert float((counts - expected).abs().max()) < 0.03
