@@ -1,0 +1,135 @@
+"""Command line in the manner of `tau-server` (crates/server/src/args.rs:346-446), for token ids instead of chat text.
+
+Options that the reference has keep its names and meanings: `-m/--model PATH`,
+`--device auto|gpu|cpu` (args.rs: auto is CUDA GPU 0; this library has no CPU path, so `cpu`
+is refused as the reference refuses bfloat16 there), `--dtype auto|f32|bf16` (auto: bf16 if
+the folder declares it), `--cuda-graph none|full`, `--prefill-chunk-size N`, `--metrics`
+(an `inference_metrics {...}` line on stderr, crates/metrics/src/serving.rs:35-54),
+`--tracing` (an `inference_trace {...}` line on stdout with prompt ids, generated ids and
+per-step logit checksums, crates/metrics/src/trace.rs:22-52,88-106; logits then go to the
+host and the host selector of crates/engine/src/generation.rs:81-95 is not needed because
+the device selector has the same semantics), and `--max-tokens N` as the output limit of a
+request (the request field `max_tokens`, crates/server/src/chat_completions_handler/
+request.rs:27-110; default: the folder's generation settings, else 16).  The server, chat
+template and MoE options have no counterpart here.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import sys
+import time
+from typing import List, Optional
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = argparse.ArgumentParser(prog="tau", description="Generate token ids with a local safetensors model on one B200.")
+    model = parser.add_argument_group("Model options")
+    model.add_argument("-m", "--model", metavar="PATH", help="Local safetensors model directory.")
+    model.add_argument("--device", default="auto", choices=["auto", "gpu", "cpu"], help="Execution device. [default: auto] auto/gpu: CUDA GPU 0; cpu is not available.")
+    model.add_argument("--dtype", default="auto", choices=["auto", "f32", "bf16", "float32", "bfloat16"],
+                       help="Model precision. [default: auto] auto: BF16 if the folder declares it, else F32. F32 is true 32-bit throughout.")
+    model.add_argument("--random-weights", metavar="CONFIG_JSON", help="Write a model folder with random weights for this config.json to --model and exit unless prompts are given.")
+    model.add_argument("--seed", type=int, default=0, help="Seed of random weights and of temperature sampling. [default: 0]")
+    model.add_argument("--norm-jitter", type=float, default=0.0, help="Random weights: norm weights are 1 + N(0, jitter). [default: 0]")
+    execution = parser.add_argument_group("Execution options")
+    execution.add_argument("--cuda-graph", default="full", choices=["none", "full"], help="CUDA graph policy for decode steps. [default: full]")
+    execution.add_argument("--prefill-chunk-size", type=int, default=8192, metavar="N", help="Most prompt tokens per prefill step, over the whole batch. [default: 8192]")
+    execution.add_argument("--max-batch", type=int, default=64, metavar="N", help="Most requests that start together. [default: 64]")
+    execution.add_argument("--cache-tokens", type=int, default=None, metavar="N", help="Tokens the cache holds (each live request rounded up to 64). [default: what the requests need]")
+    request = parser.add_argument_group("Request options")
+    request.add_argument("--prompt-ids", action="append", default=[], metavar="1,2,3", help="Token ids of one prompt; may be given several times.")
+    request.add_argument("--prompt-file", metavar="PATH", help="JSON file: a list of prompts, each a list of token ids.")
+    request.add_argument("--max-tokens", type=int, default=None, metavar="N", help="Most tokens to generate per request. [default: generation settings of the folder, else 16]")
+    request.add_argument("--temperature", type=float, default=0.0, help="0: greedy. [default: 0]")
+    request.add_argument("--stop-ids", default=None, metavar="1,2", help="Stop token ids. [default: eos_token_id of the folder]")
+    logging = parser.add_argument_group("Logging options")
+    logging.add_argument("--metrics", action="store_true", help="Log throughput to stderr. [default: off]")
+    logging.add_argument("--tracing", action="store_true", help="Log numerical traces (token ids, logit checksums) to stdout. [default: off]")
+    return parser
+
+
+def _ids(text: str) -> List[int]:
+    return [int(part) for part in text.replace(" ", "").split(",") if part]
+
+
+class _Tracer:
+    """Wraps a selector: copies each step's logits to the host and records what the reference's trace records."""
+
+    def __init__(self, select):
+        self.select, self.steps, self.started = select, [], time.perf_counter()
+
+    def __call__(self, logits, request_ids, token_indices):
+        begin = time.perf_counter()
+        tokens = self.select(logits, request_ids, token_indices)
+        host = logits.float().cpu().numpy()
+        for row, (request, index, token) in enumerate(zip(request_ids, token_indices, tokens)):
+            values = host[row]
+            finite = values[values == values]
+            self.steps.append({
+                "index": len(self.steps), "request": request, "phase": "prefill" if index == 0 else "decode", "token_index": index,
+                "token_id": int(token), "start_us": int((begin - self.started) * 1e6),
+                "logits": {"count": int(values.size), "finite_count": int((abs(finite) != float("inf")).sum()),
+                           "sha256_f32_le": hashlib.sha256(values.astype("<f4").tobytes()).hexdigest(),
+                           "selected_logit": float(values[token])},
+            })
+        return tokens
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    parser = build_parser()
+    args = parser.parse_args(argv)
+    if args.model is None:
+        parser.error("--model is required")
+    if args.prefill_chunk_size <= 0:
+        parser.error("--prefill-chunk-size must be positive")
+    if args.random_weights:
+        from .weights import write_random_model
+
+        with open(args.random_weights) as handle:
+            config = json.load(handle)
+        storage = "float32" if args.dtype in ("f32", "float32") else "bfloat16"
+        write_random_model(args.model, config, seed=args.seed, norm_jitter=args.norm_jitter, storage=storage)
+        print(f"wrote {args.model} (seed {args.seed}, {storage})", file=sys.stderr)
+    prompts = [_ids(text) for text in args.prompt_ids]
+    if args.prompt_file:
+        with open(args.prompt_file) as handle:
+            prompts += json.load(handle)
+    if not prompts:
+        if args.random_weights:
+            return 0
+        parser.error("give --prompt-ids or --prompt-file")
+
+    from .api import load_model
+    from .config.generation import GenerationConfig
+    from .engine.generate import GenerationMetrics, generate_tokens
+    from .engine.step import Engine
+    from .sampling.sampler import Sampler, SamplingParams
+
+    model = load_model(args.model, args.dtype, args.device)
+    settings: GenerationConfig = model.generation_config
+    limit = args.max_tokens if args.max_tokens is not None else settings.max_new_tokens
+    stop = _ids(args.stop_ids) if args.stop_ids is not None else settings.eos_token_ids
+    cache_tokens = args.cache_tokens
+    if cache_tokens is None:
+        needs = sorted((-(-(len(prompt) + limit) // 64) * 64 for prompt in prompts), reverse=True)
+        cache_tokens = max(64, sum(needs[: args.max_batch]))
+    engine = Engine(model, cache_tokens)
+    engine.use_graphs = engine.use_graphs and args.cuda_graph == "full"
+    select = Sampler(SamplingParams(args.temperature, args.seed)).select
+    tracer = _Tracer(select) if args.tracing else None
+    metrics = GenerationMetrics()
+    started = time.perf_counter()
+    results = generate_tokens(engine, prompts, limit, tracer or select, stop, args.max_batch, args.prefill_chunk_size, metrics)
+    elapsed = time.perf_counter() - started
+    for index, result in enumerate(results):
+        print(json.dumps({"request": index, "prompt_tokens": result.prompt_tokens, "completion_tokens": len(result.tokens),
+                          "tokens": result.tokens, "finish_reason": result.finish_reason}))
+    if tracer:
+        print("inference_trace " + json.dumps({
+            "schema": "tau_rs_b200/1", "prompts": prompts, "generated": [result.tokens for result in results], "steps": tracer.steps,
+            "summary": {"decode_tokens_per_second": metrics.decode_tokens_per_second, "elapsed_ms": elapsed * 1e3}}))
+    if args.metrics:
+        print("inference_metrics " + json.dumps(dict(metrics.as_dict(), elapsed_ms=round(elapsed * 1e3, 3))), file=sys.stderr)
+    return 0

@@ -49,7 +49,23 @@ def _on_device(*tensors) -> None:
             _require(tensor.is_contiguous() or tensor.stride(-1) == 1, "tensors must have a unit innermost stride")
 
 
-def _check(status: int, what: str) -> None:
+_launches = 0
+_replayed = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far (those inside replayed graphs included)."""
+    return _launches + _replayed
+
+
+def count_replay(kernels_in_graph: int) -> None:
+    global _replayed
+    _replayed += kernels_in_graph
+
+
+def _check(status: int, what: str, kernels_launched: int = 1) -> None:
+    global _launches
+    _launches += kernels_launched
     if status != 0:
         library = build.load_library("elementwise.cu")
         library.tau_error_string.restype = ctypes.c_char_p
@@ -139,8 +155,48 @@ def gemm_simt(values, weight, bias, out) -> None:
                                  ctypes.c_longlong(out.stride(0)), _stream()), "gemm_simt")
 
 
+SKINNY_MAX_ROWS = 32
+
+
+def _skinny_fits(values, weight, out) -> bool:
+    return (values.dtype == torch.bfloat16 and values.shape[0] <= SKINNY_MAX_ROWS and values.shape[1] % 8 == 0
+            and values.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and values.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(values, weight, bias, out) -> None:
+    """bfloat16 product for at most 32 activation rows, bound by streaming `weight` once."""
+    _on_device(values, weight, bias, out)
+    rows, depth = values.shape
+    features = weight.shape[0]
+    _require(weight.shape[1] == depth and out.shape == (rows, features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(values.dtype == weight.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32),
+             "inputs must be bfloat16 and the output bfloat16 or float32")
+    _require(_skinny_fits(values, weight, out), "needs M <= 32, K % 8 == 0 and 16-byte aligned rows")
+    _f32_vector(bias, features, "the bias")
+    library = build.load_library("gemm_skinny.cu")
+    _check(library.tau_gemm_skinny(_code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out), ctypes.c_int(rows),
+                                   ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
+                                   ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), _stream()), "gemm_skinny")
+
+
+def gemm_library(values, weight, bias, out) -> None:
+    """bfloat16 product through the vendor library (cuBLAS by way of torch), as the reference's engine does for
+    its dense projections (crates/models/src/components/cuda/decode/operation.rs:150-193)."""
+    _on_device(values, weight, bias, out)
+    _require(values.dtype == weight.dtype == out.dtype == torch.bfloat16, "the library product is used for bfloat16 only")
+    torch.mm(values, weight.t(), out=out)
+    if bias is not None:
+        out.add_(bias.to(out.dtype))
+
+
 def linear(values, weight, bias, out) -> None:
     """`out = values @ weight.T + bias` with the kernel that fits the dtype and the sizes."""
+    if values.dtype == torch.bfloat16:
+        if _skinny_fits(values, weight, out):
+            return gemm_skinny(values, weight, bias, out)
+        if out.dtype == torch.bfloat16 and values.shape[0] > SKINNY_MAX_ROWS:
+            return gemm_library(values, weight, bias, out)
     gemm_simt(values, weight, bias, out)
 
 
@@ -237,7 +293,7 @@ def argmax(logits, tokens, valid) -> None:
     scratch = _scratch_for(logits)
     library = build.load_library("sampling.cu")
     _check(library.tau_argmax(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
-                              ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax")
+                              ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax", 2)
 
 
 def sample_gumbel(logits, tokens, valid, inverse_temperature: float, seed: int, request_ids, token_indices) -> None:
@@ -251,4 +307,4 @@ def sample_gumbel(logits, tokens, valid, inverse_temperature: float, seed: int, 
     _check(library.tau_sample_gumbel(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
                                      ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid),
                                      ctypes.c_float(inverse_temperature), ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF),
-                                     _pointer(request_ids), _pointer(token_indices), _stream()), "sample_gumbel")
+                                     _pointer(request_ids), _pointer(token_indices), _stream()), "sample_gumbel", 2)

@@ -8,6 +8,7 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
     return [
         ("elementwise.cu", ()),
         ("gemm_simt.cu", ()),
+        ("gemm_skinny.cu", ()),
         ("attention_generic.cu", ()),
         ("sampling.cu", ()),
     ]

@@ -26,6 +26,7 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
         self.splits = splits
+        self.launches = 0
 
 
 def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]):
@@ -45,8 +46,11 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
             engine.model.forward(context, engine.cache)
         torch.cuda.current_stream().wait_stream(stream)
         graph = torch.cuda.CUDAGraph()
+        before = kernels.launch_count()
         with torch.cuda.graph(graph):
             state.logits = engine.model.forward(context, engine.cache)
+        state.launches = kernels.launch_count() - before
         state.graph = graph
     state.graph.replay()
+    kernels.count_replay(state.launches)
     return state.logits

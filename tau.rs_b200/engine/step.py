@@ -39,6 +39,7 @@ class Engine:
         self.cache = SequenceCache(model.cache_groups(), max_tokens, limit, model.dtype, self.device, max_slots)
         self._ring: Optional[PinnedRing] = None
         self._graphs: Dict = {}
+        self.last_step_ints = 0     # size of the last step's metadata (int32 words copied to the device)
         # A captured step runs more than once while it is captured; state that a mixer updates in place forbids that.
         self.use_graphs = self.device.type == "cuda" and not self.cache.states
 
@@ -107,6 +108,7 @@ class Engine:
         max_len = max(start + len(entry.tokens) for entry, start in zip(entries, starts))
         stride = page_stride if page_stride is not None else pages_for(max_len)
         layout = StepLayout(n_tokens, len(entries), n_wanted, {group: stride for group in self.cache.kv})
+        self.last_step_ints = layout.total
         if buffer is None:
             buffer = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         if self.device.type == "cuda":

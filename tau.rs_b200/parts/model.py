@@ -96,29 +96,21 @@ class DecoderModel:
             self.head = self.embedding
 
     def weight_bytes(self) -> int:
-        """Bytes of every distinct weight tensor that one step reads (the embedding table is read by row)."""
-        seen, total = set(), 0
+        """Bytes of every weight tensor that one step reads once (the embedding table is read by row, so it
+        counts only where it is the head as well; a block that the schedule never names is left out)."""
+        from ..weights.loader import device_dtype
 
-        def visit(part):
-            nonlocal total
-            for value in vars(part).values():
-                if isinstance(value, torch.Tensor):
-                    if value.data_ptr() not in seen:
-                        seen.add(value.data_ptr())
-                        total += value.numel() * value.element_size()
-                elif isinstance(value, (list, tuple)):
-                    for item in value:
-                        if hasattr(item, "tensor_specs"):
-                            visit(item)
-                elif hasattr(value, "tensor_specs"):
-                    visit(value)
-
-        for entry in {entry.layer for entry in self.spec.schedule}:
-            visit(self.blocks[entry])
-        visit(self.final_norm)
-        if self.head is not None and self.head.data_ptr() not in seen:
-            total += self.head.numel() * self.head.element_size()
-        return total
+        scheduled = {entry.layer for entry in self.spec.schedule}
+        total = 0
+        for index, part in enumerate((*self.blocks, self.final_norm)):
+            if index < len(self.blocks) and index not in scheduled:
+                continue
+            for spec in part.tensor_specs().values():
+                count = 1
+                for extent in spec.shape:
+                    count *= extent
+                total += count * torch.empty((), dtype=device_dtype(spec, self.dtype)).element_size()
+        return total + self.spec.vocab_size * self.spec.hidden * torch.empty((), dtype=self.dtype).element_size()
 
     # ---- forward -----------------------------------------------------------------
     def forward(self, step, cache) -> Optional[torch.Tensor]:

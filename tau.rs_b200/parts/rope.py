@@ -15,6 +15,9 @@ from .base import Part
 from .registry import register_position
 
 
+_TABLES = {}
+
+
 @register_position("rope_half")
 class RotaryTables(Part):
     def __init__(self, spec, device):
@@ -26,6 +29,10 @@ class RotaryTables(Part):
 
     def finalize_weights(self):
         spec = self.spec
+        key = (spec, str(self.device))
+        if key in _TABLES:          # layers with the same encoding share one pair of tables
+            self.cos, self.sin = _TABLES[key]
+            return
         power = torch.tensor(
             [float(spec.theta) ** (index / spec.rotary_dim) for index in range(0, spec.rotary_dim, 2)],
             dtype=torch.float64,
@@ -35,3 +42,4 @@ class RotaryTables(Part):
         angles = positions[:, None] * inverse[None, :]
         self.cos = torch.cos(angles).contiguous().to(self.device)
         self.sin = torch.sin(angles).contiguous().to(self.device)
+        _TABLES[key] = (self.cos, self.sin)

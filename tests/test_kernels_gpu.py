@@ -92,6 +92,20 @@ def test_gemm_simt(dtype, out_dtype, m, n, k):
         close(found, wanted, out_dtype)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k", [(1, 16, 8), (8, 100, 72), (3, 17, 4096), (9, 33, 520), (16, 256, 128), (17, 40, 200), (32, 1000, 64)])
+def test_gemm_skinny(out_dtype, m, n, k):
+    values = randn(m, k + 8, dtype=torch.bfloat16, seed=15)[:, :k]     # rows wider than K
+    weight = randn(n, k, dtype=torch.bfloat16, seed=16)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(17)).to(DEVICE)
+    for use_bias in (None, bias):
+        found = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
+        wanted = torch.empty(m, n, dtype=out_dtype)
+        kernels.gemm_skinny(values, weight, use_bias, found)
+        plain_kernels.linear(values.cpu(), weight.cpu(), None if use_bias is None else use_bias.cpu(), wanted)
+        close(found, wanted, out_dtype)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_dispatch_matches_plain(dtype):
     """Whatever kernel `linear` picks for a shape, the product is the same: ragged and aligned shapes, views of a stack."""

@@ -1,0 +1,272 @@
+"""Each part alone against its plain function, and a toy architecture assembled from a mixer that the test defines."""
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from tau_rs_b200 import Engine, StepEntry, load_model, write_random_model
+from tau_rs_b200.cache import SequenceCache
+from tau_rs_b200.config import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry, SwiGLUSpec,
+                                register_architecture, unregister_architecture)
+from tau_rs_b200.engine.batch import StepLayout, fill_step, step_views
+from tau_rs_b200.parts import CacheNeed, Mixer, build, register_mixer, unregister
+from tau_rs_b200.weights import TensorSpec, random_tensors
+
+pytestmark = pytest.mark.gpu
+DEVICE = torch.device("cuda:0")
+TOLERANCE = {torch.float32: 2e-5, torch.bfloat16: 1.5e-2}
+
+
+def error(found, wanted):
+    return float((found.double().cpu() - wanted.double()).abs().max() / wanted.double().abs().max())
+
+
+def fill(part, dtype, seed=0, jitter=0.1):
+    """Random weights for one part; returns them (as float32 on the host, rounded through the part's dtype)."""
+    plain = {}
+    for name, tensor, spec in random_tensors(part.tensor_specs(), seed, jitter):
+        stored = tensor.to(dtype) if spec.role == "matrix" else tensor
+        part.assign(name, stored.to(DEVICE))
+        plain[name] = stored.float()
+    part.finalize_weights()
+    return plain
+
+
+def rounding(dtype):
+    return plain_model.bfloat16_rounding if dtype == torch.bfloat16 else plain_model.no_rounding
+
+
+def single_sequence_step(cache, slot, count, start=0):
+    entry = StepEntry(slot, [0] * count, [])
+    cache.reserve(slot, start + count)
+    layout = StepLayout(count, 1, 0, {group: (start + count + 63) // 64 for group in cache.kv})
+    staged = np.zeros(layout.total, dtype=np.int32)
+    fill_step(layout, staged, [entry], [start], cache)
+    step = step_views(layout, torch.from_numpy(staged).to(DEVICE), count, start + count, count == 1)
+    cache.advance(slot, start + count)
+    return step
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    spec = NormSpec(width=200, eps=3e-4)
+    part = build("norm", spec, name="n.weight", dtype=dtype, device=DEVICE)
+    plain = fill(part, dtype)
+    x = torch.randn(9, 200).to(dtype)
+    branch = torch.randn(9, 200).to(dtype)
+    assert error(part.forward(x.to(DEVICE)), plain_model.rms_norm(x.float(), plain["n.weight"], 3e-4, rounding(dtype))) < TOLERANCE[dtype]
+    residual = x.to(DEVICE).clone()
+    normed = part.add_forward(branch.to(DEVICE), residual)
+    summed = rounding(dtype)(x.float() + branch.float())
+    assert torch.equal(residual.float().cpu(), summed)
+    assert error(normed, plain_model.rms_norm(summed, plain["n.weight"], 3e-4, rounding(dtype))) < TOLERANCE[dtype]
+
+
+def test_rotary_tables_part():
+    spec = PositionSpec(rotary_dim=48, theta=50000.0, max_positions=300)
+    part = build("position", spec, device=DEVICE)
+    part.finalize_weights()
+    cos, sin = plain_model.rope_tables(48, 50000.0, 300)
+    assert torch.equal(part.cos.cpu(), cos) and torch.equal(part.sin.cpu(), sin)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    spec = SwiGLUSpec(hidden=72, intermediate=200)
+    part = build("feed_forward", spec, prefix="ff", dtype=dtype, device=DEVICE)
+    plain = fill(part, dtype)
+    x = torch.randn(70, 72).to(dtype)
+    found = part.forward(x.to(DEVICE), None)
+    assert error(found, plain_model.swiglu(x.float(), plain, "ff", rounding(dtype))) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,groups,width,bias", [(6, 2, 32, True), (3, 3, 80, False)])
+def test_attention_part_whole_then_stepwise(dtype, heads, groups, width, bias):
+    hidden = 56
+    spec = AttentionSpec(hidden=hidden, n_heads=heads, n_kv_heads=groups, head_dim=width, bias=bias, softmax_scale=width ** -0.5,
+                         qk_norm=NormSpec(width=width, eps=1e-5), position=PositionSpec(rotary_dim=width, theta=1e4, max_positions=256))
+    part = build("mixer", spec, prefix="attn", dtype=dtype, device=DEVICE)
+    plain = fill(part, dtype)
+    config = plain_model.PlainConfig(vocab_size=1, hidden_size=hidden, intermediate_size=1, num_hidden_layers=1, num_attention_heads=heads,
+                                     num_key_value_heads=groups, head_dim=width, attention_bias=bias, rms_norm_eps=1e-5, rope_theta=1e4,
+                                     max_position_embeddings=256, tie_word_embeddings=True)
+    cos, sin = plain_model.rope_tables(width, 1e4, 256)
+    x = torch.randn(90, hidden).to(dtype)
+    wanted = plain_model.attention_mixer(x.float(), plain, "attn", config, cos, sin, rounding(dtype))
+    cache = SequenceCache({"g": (part.cache_need(), 1)}, 256, 256, dtype, DEVICE)
+    slot = cache.open()
+    view = cache.layer_view("g", 0)
+    found = [part.forward(x[:70].to(DEVICE), single_sequence_step(cache, slot, 70), view, True)]
+    for position in range(70, 90):
+        found.append(part.forward(x[position : position + 1].to(DEVICE), single_sequence_step(cache, slot, 1, position), view, True))
+    assert error(torch.cat(found), wanted) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_part(dtype):
+    hidden = 48
+    norm = NormSpec(width=hidden, eps=1e-6)
+    attention = AttentionSpec(hidden=hidden, n_heads=4, n_kv_heads=1, head_dim=16, bias=False, softmax_scale=0.25,
+                              qk_norm=NormSpec(width=16, eps=1e-6), position=PositionSpec(rotary_dim=16, theta=1e4, max_positions=128))
+    spec = BlockSpec(prefix="model.layers.0", mixer=attention, feed_forward=SwiGLUSpec(hidden=hidden, intermediate=100),
+                     mixer_norm=norm, feed_forward_norm=norm)
+    part = build("block", spec, dtype=dtype, device=DEVICE)
+    plain = fill(part, dtype)
+    config = plain_model.PlainConfig(vocab_size=1, hidden_size=hidden, intermediate_size=100, num_hidden_layers=1, num_attention_heads=4,
+                                     num_key_value_heads=1, head_dim=16, attention_bias=False, rms_norm_eps=1e-6, rope_theta=1e4,
+                                     max_position_embeddings=128, tie_word_embeddings=True)
+    cos, sin = plain_model.rope_tables(16, 1e4, 128)
+    x = torch.randn(33, hidden).to(dtype)
+    wanted = plain_model.decoder_block(x.float(), plain, "model.layers.0", config, cos, sin, rounding(dtype))
+    cache = SequenceCache({"g": (part.cache_need(), 1)}, 128, 128, dtype, DEVICE)
+    slot = cache.open()
+    residual, branch = part.forward(x.to(DEVICE).clone(), None, single_sequence_step(cache, slot, 33), cache.layer_view("g", 0), True)
+    found = rounding(dtype)(residual.float().cpu() + branch.float().cpu())
+    assert error(found, wanted) < TOLERANCE[dtype]
+
+
+# ------------------------------------------------------------------------------------------------
+# A toy mixer with state of its own, defined here, registered, built and stepped without touching the library.
+class DecaySpec:
+    kind = "toy_decay"
+
+    def __init__(self, hidden, decay):
+        self.hidden, self.decay = hidden, decay
+
+    def __eq__(self, other):
+        return isinstance(other, DecaySpec) and (self.hidden, self.decay) == (other.hidden, other.decay)
+
+    def __hash__(self):
+        return hash((self.hidden, self.decay))
+
+
+class DecayMixer(Mixer):
+    """`s_t = decay * s_{t-1} + x_t W^T`, `y_t = s_t`: one vector of state per sequence, whatever its length."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        self.weight = None
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.spec.hidden,), state_dtype=torch.float32)
+
+    def tensor_specs(self):
+        return {f"{self.prefix}.mix.weight": TensorSpec((self.spec.hidden, self.spec.hidden), role="matrix", std=0.1)}
+
+    def assign(self, name, tensor):
+        self.weight = tensor
+
+    def forward(self, hidden, step, cache, writes_cache):
+        projected = hidden.float() @ self.weight.float().t()
+        out = torch.empty_like(projected)
+        bounds, slots = step.cu_seqlens.cpu().tolist(), step.seq_slot.cpu().tolist()
+        for index, slot in enumerate(slots):
+            state = cache.state[slot]
+            for row in range(bounds[index], bounds[index + 1]):
+                state.mul_(self.spec.decay).add_(projected[row])
+                out[row] = state
+        return out.to(hidden.dtype)
+
+
+def toy_spec(config) -> ModelSpec:
+    hidden = config["hidden_size"]
+    norm = NormSpec(width=hidden, eps=config["eps"])
+    attention = AttentionSpec(hidden=hidden, n_heads=4, n_kv_heads=2, head_dim=16, bias=False, softmax_scale=0.25,
+                              qk_norm=None, position=PositionSpec(rotary_dim=8, theta=100.0, max_positions=config["max_positions"]))
+    feed = SwiGLUSpec(hidden=hidden, intermediate=config["intermediate_size"])
+    blocks = (
+        BlockSpec("toy.layers.0", DecaySpec(hidden, 0.9), feed, norm, norm),
+        BlockSpec("toy.layers.1", attention, feed, norm, norm),
+    )
+    schedule = (
+        ScheduleEntry(layer=0, cache_group="decay", cache_layer=0),
+        ScheduleEntry(layer=1, cache_group="keys", cache_layer=0),
+        ScheduleEntry(layer=0, cache_group="decay", cache_layer=1),                    # the same weights again, state of its own
+        ScheduleEntry(layer=1, cache_group="keys", cache_layer=0, writes_cache=False), # reads the keys the earlier run wrote
+    )
+    return ModelSpec(architecture="ToyForCausalLM", vocab_size=config["vocab_size"], hidden=hidden, max_positions=config["max_positions"],
+                     embedding_name="toy.embed.weight", blocks=blocks, schedule=schedule, final_norm=norm,
+                     final_norm_name="toy.norm.weight", head_name="toy.head.weight", tie_head=False)
+
+
+@pytest.fixture
+def toy_architecture():
+    register_mixer("toy_decay")(DecayMixer)
+    register_architecture("ToyForCausalLM", "toy", lambda raw: raw, toy_spec)
+    yield
+    unregister_architecture("ToyForCausalLM")
+    unregister("mixer", "toy_decay")
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture, tmp_path):
+    config = {"architectures": ["ToyForCausalLM"], "model_type": "toy", "hidden_size": 40, "intermediate_size": 72, "vocab_size": 97,
+              "max_positions": 200, "eps": 1e-5}
+    folder = str(tmp_path / "toy")
+    write_random_model(folder, config, seed=4, norm_jitter=0.1, storage="float32")
+    model = load_model(folder, "float32", DEVICE)
+    assert set(model.cache_groups()) == {"decay", "keys"}
+    assert model.cache_groups()["decay"][1] == 2 and model.cache_groups()["keys"][1] == 1
+    engine = Engine(model, 64 * 6)
+    assert not engine.use_graphs                      # state that is updated in place is never replayed
+    rng = np.random.default_rng(0)
+    requests = [rng.integers(0, 97, size=length).tolist() for length in (70, 9, 33)]
+
+    def whole(tokens):
+        slot = engine.open_sequence()
+        logits = engine.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().clone()
+        engine.close_sequence(slot)
+        return logits
+
+    alone = [whole(tokens) for tokens in requests]
+    # The same requests as a batch of unequal lengths: prompts first, then token by token, on slots used before.
+    slots = [engine.open_sequence() for _ in requests]
+    prompt_lengths = [40, 5, 33]
+    logits = engine.step([StepEntry(slot, tokens[:cut], [cut - 1]) for slot, tokens, cut in zip(slots, requests, prompt_lengths)]).cpu()
+    for row, cut in enumerate(prompt_lengths):
+        assert error(logits[row], alone[row][cut - 1]) < 1e-4
+    for offset in range(4):
+        live = [index for index in range(3) if prompt_lengths[index] + offset < len(requests[index])]
+        logits = engine.step([StepEntry(slots[i], [requests[i][prompt_lengths[i] + offset]], [0]) for i in live]).cpu()
+        for row, i in enumerate(live):
+            assert error(logits[row], alone[i][prompt_lengths[i] + offset]) < 1e-4
+    for slot in slots:
+        engine.close_sequence(slot)
+    engine.cache.check()
+    # Independent check of the whole model against plain functions for its parts.
+    weights = plain_model.read_plain_weights(folder)
+    tokens = requests[0]
+    hidden = plain_model.embedding(weights["toy.embed.weight"], tokens)
+    cos, sin = plain_model.rope_tables(8, 100.0, 200)
+    keys_seen = {}
+
+    def decay_run(x, prefix):
+        projected = x @ weights[f"{prefix}.self_attn.mix.weight"].t()
+        state, rows = torch.zeros(40), []
+        for row in projected:
+            state = 0.9 * state + row
+            rows.append(state)
+        return torch.stack(rows)
+
+    def attention_run(x, prefix, reuse):
+        count = x.shape[0]
+        q = (x @ weights[f"{prefix}.self_attn.q_proj.weight"].t()).view(count, 4, 16)
+        rotate = lambda t: torch.cat([plain_model.apply_rope(t[..., :8], cos[:count], sin[:count], plain_model.no_rounding), t[..., 8:]], dim=-1)
+        if not reuse:
+            k = (x @ weights[f"{prefix}.self_attn.k_proj.weight"].t()).view(count, 2, 16)
+            v = (x @ weights[f"{prefix}.self_attn.v_proj.weight"].t()).view(count, 2, 16)
+            keys_seen["k"], keys_seen["v"] = rotate(k), v
+        context = plain_model.causal_attention(rotate(q), keys_seen["k"], keys_seen["v"], plain_model.no_rounding)
+        return context.reshape(count, 64) @ weights[f"{prefix}.self_attn.o_proj.weight"].t()
+
+    for layer, reuse in ((0, False), (1, False), (0, False), (1, True)):
+        prefix = f"toy.layers.{layer}"
+        normed = plain_model.rms_norm(hidden, weights[f"{prefix}.input_layernorm.weight"], 1e-5, plain_model.no_rounding)
+        hidden = hidden + (decay_run(normed, prefix) if layer == 0 else attention_run(normed, prefix, reuse))
+        normed = plain_model.rms_norm(hidden, weights[f"{prefix}.post_attention_layernorm.weight"], 1e-5, plain_model.no_rounding)
+        hidden = hidden + plain_model.swiglu(normed, weights, f"{prefix}.mlp", plain_model.no_rounding)
+    expected = plain_model.rms_norm(hidden, weights["toy.norm.weight"], 1e-5, plain_model.no_rounding) @ weights["toy.head.weight"].t()
+    assert error(alone[0], expected) < 1e-4
