@@ -25,7 +25,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 _BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-shared",
                "--expt-relaxed-constexpr", "-Xcompiler", "-fvisibility=hidden"]
-_HEADERS = ("common.cuh",)
+_HEADERS = tuple(sorted(name for name in os.listdir(_HERE) if name.endswith((".cuh", ".h"))))
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
