@@ -160,3 +160,54 @@ TAU_EXPORT int tau_sample_gumbel(const float* logits, int rows, int vocab, unsig
     merge_best_kernel<<<rows, kThreads, 0, s>>>(scratch, chunks, tokens, valid);
     return tau_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in sampling_static.h).
+#include "sampling_static.h"
+
+namespace {
+
+// Scratch of the static variant.  In host code this name is only a stand-in for the symbol: the device
+// address comes from cudaGetSymbolAddress, once per device, and that address is what the kernels get.
+static __device__ __align__(256) unsigned static_scratch[TAU_ARGMAX_STATIC_WORDS];
+
+constexpr int kMaxDevices = 64;
+unsigned* static_scratch_address[kMaxDevices] = {};
+
+}  // namespace
+
+TAU_EXPORT long long tau_argmax_static_words_needed(int rows, int vocab) { return tau_select_scratch_words(rows, vocab); }
+
+TAU_EXPORT const char* tau_argmax_static_error(int code) {
+    switch (code) {
+        case 0: return "no error";
+        case TAU_ARGMAX_STATIC_TOO_LARGE: return "rows * ceil(vocab / 2048) * 3 exceeds the static scratch of 24576 words";
+        case TAU_ARGMAX_STATIC_BAD_ARGUMENT: return "null pointer, or rows or vocab not positive";
+        case TAU_ARGMAX_STATIC_BAD_DEVICE: return "the current device number is 64 or more";
+        default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown code";
+    }
+}
+
+TAU_EXPORT int tau_argmax_static(const float* logits, int rows, int vocab, int* tokens, int* valid, void* stream) {
+    if (!logits || !tokens || !valid || rows <= 0 || vocab <= 0) return TAU_ARGMAX_STATIC_BAD_ARGUMENT;
+    if (tau_select_scratch_words(rows, vocab) > TAU_ARGMAX_STATIC_WORDS) return TAU_ARGMAX_STATIC_TOO_LARGE;
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return static_cast<int>(status);
+    if (device < 0 || device >= kMaxDevices) return TAU_ARGMAX_STATIC_BAD_DEVICE;
+    if (!static_scratch_address[device]) {  // set-up: first call on this device, with this device current
+        unsigned* address = nullptr;
+        status = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), static_scratch);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        static_scratch_address[device] = address;
+    }
+    unsigned* scratch = static_scratch_address[device];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
+    // Writes scratch[0 .. rows * chunks * 3): every word that the merge below reads.
+    chunk_best_kernel<false><<<dim3(chunks, rows), kThreads, 0, s>>>(logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
+    int launched = tau_launch_status();
+    if (launched) return launched;
+    merge_best_kernel<<<rows, kThreads, 0, s>>>(scratch, chunks, tokens, valid);
+    return tau_launch_status();
+}
