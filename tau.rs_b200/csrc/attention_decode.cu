@@ -1,0 +1,285 @@
+// Decode attention: one new token per sequence over its cached context, split along the context.
+//
+// Compiled for one head size and dtype (-DTAU_HEAD_DIM=..., -DTAU_DTYPE=0|1), so a model compiles the one
+// variant it needs.  Reference counterpart: crates/cuda-kernels/src/kernels/decode_attention.cu:186-250
+// (`attention`: grid (heads, splits), 32-bit dot per key, `* rsqrt(d)`, max, exp, sum, probabilities times V)
+// and :255-278 (`combine_attention`: merge of the splits' (max, sum, context) records).  Here a block serves
+// one KV head of one sequence and all the query heads of its group at once, so keys and values are read once
+// for the group; lengths and page lists are per sequence and come from device memory, so one captured graph
+// serves every step.
+//
+// grid (splits, n_kv_heads * passes, sequences); a pass covers up to 8 query heads of a group.
+// Partial results go to scratch: o[seq][head][split][D] (not normalised) and ml[seq][head][split][2] (max, sum).
+#include "common.cuh"
+
+#ifndef TAU_HEAD_DIM
+#error "compile with -DTAU_HEAD_DIM=<multiple of 16 up to 256>"
+#endif
+#ifndef TAU_DTYPE
+#error "compile with -DTAU_DTYPE=0 (float32) or 1 (bfloat16)"
+#endif
+
+namespace {
+
+constexpr int D = TAU_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head_dim must be a multiple of 16 between 16 and 256");
+#if TAU_DTYPE == 1
+typedef bf16 T;
+constexpr int kVec = 8;   // elements per 16-byte load
+#else
+typedef float T;
+constexpr int kVec = 4;
+#endif
+constexpr int kWarps = 4;
+#if TAU_DTYPE == 1
+__device__ __forceinline__ float exponential(float value) { return __expf(value); }
+#else
+__device__ __forceinline__ float exponential(float value) { return expf(value); }   // the 32-bit path keeps the accurate one
+#endif
+constexpr int PER = (D + 31) / 32;            // value columns per lane
+constexpr bool kContiguous = (D % 32 == 0);   // lane owns PER neighbouring columns, else columns lane, lane + 32, ...
+
+__device__ __forceinline__ void load_vec(const T* source, float (&out)[kVec]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(source);
+#if TAU_DTYPE == 1
+    const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // a bfloat16 is the upper half of a float
+        out[2 * i] = __uint_as_float(words[i] << 16);
+        out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+#else
+    out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+    out[2] = __uint_as_float(raw.z); out[3] = __uint_as_float(raw.w);
+#endif
+}
+
+__device__ __forceinline__ int column_of(int lane, int i) { return kContiguous ? lane * PER + i : lane + 32 * i; }
+
+__device__ __forceinline__ void load_columns(const T* row, int lane, float (&out)[PER]) {
+    if constexpr (kContiguous && PER * sizeof(T) == 16) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row + lane * PER);
+        const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+#if TAU_DTYPE == 1
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { out[2 * i] = __uint_as_float(words[i] << 16); out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u); }
+#else
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = __uint_as_float(words[i]);
+#endif
+    } else if constexpr (kContiguous && PER * sizeof(T) == 8) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(row + lane * PER);
+#if TAU_DTYPE == 1
+        out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+        out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+#else
+        out[0] = __uint_as_float(raw.x); out[1] = __uint_as_float(raw.y);
+#endif
+    } else {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = column_of(lane, i);
+            out[i] = c < D ? to_float(row[c]) : 0.0f;
+        }
+    }
+}
+
+template <int GH>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_partial_kernel(const T* __restrict__ queries, const T* __restrict__ keys, const T* __restrict__ values,
+                      T* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                      const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
+                      int n_heads, int n_kv_heads, int passes, float scale, int window, int splits) {
+    __shared__ __align__(16) float q_shared[GH][D];
+    __shared__ float merge_o[kWarps][GH][D];
+    __shared__ float merge_ml[kWarps][GH][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int split = blockIdx.x, seq = blockIdx.z;
+    const int kv_head = blockIdx.y / passes, pass = blockIdx.y % passes;
+    const int group = n_heads / n_kv_heads;
+    const int head0 = kv_head * group + pass * GH;                      // first query head of this block
+    const int heads_here = min(GH, group - pass * GH);                  // > 0 by construction of `passes`
+    const int length = seq_len[seq];
+    const int first = (window > 0 && length > window) ? length - window : 0;
+    const int span = length - first;
+    const int per_split = ((span + splits - 1) / splits + 31) / 32 * 32;
+    const int lo = first + split * per_split;
+    const int hi = min(length, lo + per_split);
+    const size_t record = (static_cast<size_t>(seq) * n_heads + head0) * splits + split;   // + h * splits per head
+
+    if (lo >= hi) {   // nothing for this split: an empty record
+        if (splits > 1 && threadIdx.x < heads_here) {
+            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2] = -INFINITY;
+            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2 + 1] = 0.0f;
+        }
+        return;
+    }
+    for (int index = threadIdx.x; index < GH * D; index += kWarps * 32) {
+        const int h = index / D, e = index % D;
+        q_shared[h][e] = h < heads_here ? to_float(queries[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + e]) * scale : 0.0f;
+    }
+    __syncthreads();
+
+    const int* pages = page_rows + static_cast<size_t>(seq) * page_stride;
+    const size_t head_stride = static_cast<size_t>(page_tokens) * D;
+    float running_max[GH], running_sum[GH], acc[GH][PER];
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+        running_max[h] = -INFINITY;
+        running_sum[h] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[h][i] = 0.0f;
+    }
+
+    for (int start = lo + warp * 32; start < hi; start += kWarps * 32) {
+        const int key = start + lane;
+        const bool live = key < hi;
+        float score[GH];
+#pragma unroll
+        for (int h = 0; h < GH; ++h) score[h] = 0.0f;
+        if (live) {
+            const int page = pages[key / page_tokens];
+            const T* key_row = keys + (static_cast<size_t>(page) * n_kv_heads + kv_head) * head_stride +
+                               static_cast<size_t>(key % page_tokens) * D;
+#pragma unroll 4
+            for (int e = 0; e < D; e += kVec) {
+                float k[kVec];
+                load_vec(key_row + e, k);
+#pragma unroll
+                for (int h = 0; h < GH; ++h) {
+#pragma unroll
+                    for (int i = 0; i < kVec; i += 4) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(&q_shared[h][e + i]);
+                        score[h] = fmaf(k[i], q4.x, score[h]);
+                        score[h] = fmaf(k[i + 1], q4.y, score[h]);
+                        score[h] = fmaf(k[i + 2], q4.z, score[h]);
+                        score[h] = fmaf(k[i + 3], q4.w, score[h]);
+                    }
+                }
+            }
+        }
+        float weight[GH];
+#pragma unroll
+        for (int h = 0; h < GH; ++h) {
+            const float s = live ? score[h] : -INFINITY;
+            const float new_max = fmaxf(running_max[h], warp_max(s));   // finite: lane 0 of the group is live
+            const float correction = exponential(running_max[h] - new_max);
+            weight[h] = live ? exponential(s - new_max) : 0.0f;
+            running_sum[h] = running_sum[h] * correction + warp_sum(weight[h]);
+            running_max[h] = new_max;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) acc[h][i] *= correction;
+        }
+        const int count = min(32, hi - start);
+        for (int j = 0; j < count; ++j) {
+            const int key_j = start + j;
+            const int page = pages[key_j / page_tokens];
+            const T* value_row = values + (static_cast<size_t>(page) * n_kv_heads + kv_head) * head_stride +
+                                 static_cast<size_t>(key_j % page_tokens) * D;
+            float v[PER];
+            load_columns(value_row, lane, v);
+#pragma unroll
+            for (int h = 0; h < GH; ++h) {
+                const float w = __shfl_sync(0xffffffffu, weight[h], j);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) acc[h][i] = fmaf(w, v[i], acc[h][i]);
+            }
+        }
+    }
+    // Merge the warps.
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = column_of(lane, i);
+            if (c < D) merge_o[warp][h][c] = acc[h][i];
+        }
+        if (lane == 0) {
+            merge_ml[warp][h][0] = running_max[h];
+            merge_ml[warp][h][1] = running_sum[h];
+        }
+    }
+    __syncthreads();
+    for (int index = threadIdx.x; index < heads_here * D; index += kWarps * 32) {
+        const int h = index / D, c = index % D;
+        float total_max = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) total_max = fmaxf(total_max, merge_ml[w][h][0]);
+        float o = 0.0f, sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float factor = exponential(merge_ml[w][h][0] - total_max);   // 0 for a warp that saw no key
+            o += merge_o[w][h][c] * factor;
+            sum += merge_ml[w][h][1] * factor;
+        }
+        if (splits == 1) {
+            out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = from_float<T>(o / sum);
+        } else {
+            const size_t slot = record + static_cast<size_t>(h) * splits;
+            partial_o[slot * D + c] = o;
+            if (c == 0) {
+                partial_ml[slot * 2] = total_max;
+                partial_ml[slot * 2 + 1] = sum;
+            }
+        }
+    }
+}
+
+__global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                      T* __restrict__ out, int n_heads, int splits) {
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const size_t base = (static_cast<size_t>(seq) * n_heads + head) * splits;
+    float total_max = -INFINITY;
+    for (int s = 0; s < splits; ++s) total_max = fmaxf(total_max, partial_ml[(base + s) * 2]);
+    float sum = 0.0f;
+    for (int s = 0; s < splits; ++s) sum += partial_ml[(base + s) * 2 + 1] * exponential(partial_ml[(base + s) * 2] - total_max);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float o = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float factor = exponential(partial_ml[(base + s) * 2] - total_max);
+            if (factor > 0.0f) o += partial_o[(base + s) * D + c] * factor;   // an empty split wrote no context
+        }
+        out[(static_cast<size_t>(seq) * n_heads + head) * D + c] = from_float<T>(o / sum);
+    }
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_attention_decode_head_dim() { return D; }
+TAU_EXPORT int tau_attention_decode_dtype() { return TAU_DTYPE; }
+
+// Floats of scratch that a launch needs.
+TAU_EXPORT long long tau_attention_decode_scratch(int n_seqs, int n_heads, int splits) {
+    return splits <= 1 ? 0 : static_cast<long long>(n_seqs) * n_heads * splits * (D + 2);
+}
+
+TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const void* values, void* out, const int* seq_len,
+                                    const int* page_rows, int page_stride, int page_tokens, int n_seqs, int n_heads, int n_kv_heads,
+                                    float scale, int window, int splits, float* scratch, long long scratch_floats, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (!queries || !keys || !values || !out || !seq_len || !page_rows || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
+        page_tokens <= 0 || window < 0 || splits < 1 || splits > 256 ||
+        (splits > 1 && (!scratch || scratch_floats < tau_attention_decode_scratch(n_seqs, n_heads, splits))))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int group = n_heads / n_kv_heads;
+    const int gh = group >= 8 ? 8 : group > 2 ? 4 : group;      // heads per pass: 1, 2, 4 or 8
+    const int passes = (group + gh - 1) / gh;
+    const dim3 grid(splits, n_kv_heads * passes, n_seqs);
+    float* partial_o = scratch;
+    float* partial_ml = scratch ? scratch + static_cast<size_t>(n_seqs) * n_heads * splits * D : nullptr;
+#define TAU_LAUNCH(GH)                                                                                                          \
+    decode_partial_kernel<GH><<<grid, kWarps * 32, 0, s>>>(static_cast<const T*>(queries), static_cast<const T*>(keys),          \
+                                                          static_cast<const T*>(values), static_cast<T*>(out), partial_o, partial_ml, \
+                                                          seq_len, page_rows, page_stride, page_tokens, n_heads, n_kv_heads, passes,   \
+                                                          scale, window, splits)
+    if (gh == 1) TAU_LAUNCH(1);
+    else if (gh == 2) TAU_LAUNCH(2);
+    else if (gh == 4) TAU_LAUNCH(4);
+    else TAU_LAUNCH(8);
+#undef TAU_LAUNCH
+    int status = tau_launch_status();
+    if (status || splits == 1) return status;
+    decode_combine_kernel<<<dim3(n_heads, n_seqs), D < 128 ? D : 128, 0, s>>>(partial_o, partial_ml, static_cast<T*>(out), n_heads, splits);
+    return tau_launch_status();
+}

@@ -255,13 +255,55 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
 
 
 def decode_splits(n_seqs: int, max_len: int) -> int:
-    """Number of context splits that decode attention uses for this many sequences of at most this length."""
-    return 1
+    """Number of context splits that decode attention uses for this many sequences of at most this length.
+
+    The length is rounded up to a power of two first, so that a captured graph (whose key holds this
+    number) serves a whole range of lengths; a split covers at least 128 positions.
+    """
+    bucket = 1 << max(0, (max_len - 1).bit_length())
+    return max(1, min(bucket // 128, 1024 // max(1, n_seqs), 64))
+
+
+_decode_scratch = {}
+
+
+def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                     window: int, splits: int) -> None:
+    """One query token per sequence (its last position) over `seq_len` cached positions, split along the context."""
+    _on_device(queries, keys, values, out, seq_len, page_rows)
+    n_seqs = queries.shape[0]
+    _require(queries.shape == (n_seqs, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.is_contiguous()
+             and out.dtype == queries.dtype == keys.dtype == values.dtype, "queries and output must be [sequences, n_heads * head_dim]")
+    _require(head_dim % 16 == 0 and 16 <= head_dim <= 256, "head_dim must be a multiple of 16 between 16 and 256")
+    _require(n_heads % n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads")
+    _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
+             and values.shape == keys.shape, "cache pages must be [pages, n_kv_heads, 64, head_dim]")
+    _int_vector(seq_len, "sequence lengths")
+    _require(seq_len.numel() == n_seqs and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
+             and page_rows.shape[0] == n_seqs, "one length and one row of pages per sequence")
+    _require(1 <= splits <= 256, "splits must lie between 1 and 256")
+    library = build.load_library("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={_code(queries)}"))
+    library.tau_attention_decode_scratch.restype = ctypes.c_longlong
+    floats = library.tau_attention_decode_scratch(ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(splits))
+    scratch = None
+    if floats:
+        key = (queries.device, torch.cuda.current_stream().cuda_stream)
+        scratch = _decode_scratch.get(key)
+        if scratch is None or scratch.numel() < floats:
+            scratch = _decode_scratch[key] = torch.empty(floats, dtype=torch.float32, device=queries.device)
+    _check(library.tau_attention_decode(
+        _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(seq_len), _pointer(page_rows),
+        ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+        ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(splits), _pointer(scratch),
+        ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream()), "attention_decode", 1 if splits == 1 else 2)
 
 
 def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
               window: int) -> None:
     """Causal attention of the step's tokens over their sequences' cache pages (which hold the step's own keys already)."""
+    if step.all_single:
+        splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
+        return attention_decode(queries, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits)
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
 
 

@@ -11,4 +11,7 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("gemm_skinny.cu", ()),
         ("attention_generic.cu", ()),
         ("sampling.cu", ()),
+        # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.
+        *[("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={dtype}"))
+          for head_dim in (128, 16, 32, 48) for dtype in (0, 1)],
     ]

@@ -238,6 +238,25 @@ def test_decode_attention_finds_a_far_key(dtype, n_heads, n_kv_heads, head_dim):
         assert torch.allclose(got, values[page, 0, place % 64].float(), atol=0.05, rtol=0.05)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (3, 3, 32, 0), (10, 2, 64, 0), (16, 1, 16, 0), (12, 4, 96, 0), (8, 2, 256, 0), (4, 1, 128, 100)])
+def test_decode_attention_splits_and_groups(dtype, n_heads, n_kv_heads, head_dim, window):
+    """Every number of splits gives the same context: groups of 1, 3, 4, 5 and 16 heads, splits that are empty
+    for short sequences, a window."""
+    lengths = [1, 33, 300, 129, 64]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, [1] * 5, n_kv_heads, head_dim, dtype, seed=60, pages=24)
+    queries = randn(5, n_heads * head_dim, dtype=dtype, seed=61)
+    seq_len = torch.tensor(lengths, dtype=torch.int32, device=DEVICE)
+    wanted = torch.empty(5, n_heads * head_dim, dtype=dtype)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
+    for splits in (1, 2, 5, 16):
+        found = torch.full_like(queries, float("nan"))
+        kernels.attention_decode(queries, keys, values, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window, splits)
+        close(found, wanted, dtype)
+
+
 def adversarial_rows():
     nan, inf = float("nan"), float("inf")
     rows = [
