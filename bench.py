@@ -106,6 +106,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (named in the record)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    parser.add_argument("--sections", default="prefill,decode,points,e2e", help="which measurements to run (for profiling a part alone)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -148,6 +149,10 @@ def main() -> int:
         torch.cuda.synchronize()
         return start.elapsed_time(stop)
 
+    sections = set(args.sections.split(","))
+    if args.skip_points:
+        sections.discard("points")
+
     # ---- prefill of one 2,048-token prompt ------------------------------------------------
     engine = fresh_engine(1)
     (prompt,) = prompts(1)
@@ -157,12 +162,14 @@ def main() -> int:
         engine.step([StepEntry(slot, prompt, [PROMPT_TOKENS - 1])])
         engine.close_sequence(slot)
 
-    for _ in range(2):
-        one_prefill()
-    prefill_ms = min(timed(one_prefill) for _ in range(3))
-    flops = prefill_flops(config, args.layers, PROMPT_TOKENS)
-    prefill = {"value": round(PROMPT_TOKENS / prefill_ms * 1e3, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
-               "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    prefill = None
+    if "prefill" in sections:
+        for _ in range(3):
+            one_prefill()
+        prefill_ms = min(timed(one_prefill) for _ in range(3))
+        flops = prefill_flops(config, args.layers, PROMPT_TOKENS)
+        prefill = {"value": round(PROMPT_TOKENS / prefill_ms * 1e3, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
+                   "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "of": peaks["source"]}
     del engine
 
     # ---- decode -----------------------------------------------------------------------------
@@ -206,19 +213,21 @@ def main() -> int:
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
 
     points = {}
-    if not args.skip_points:
+    if "points" in sections:
         for batch, steps in ((1, max(16, args.steps // 2)), (64, max(16, args.steps // 2))):
             point_elapsed, _, _, _, _ = decode_run(batch, steps, 3)
             points[f"decode_b{batch}"] = round(batch * steps / (point_elapsed * 1e-3), 1)
 
     # ---- end to end through generate(): host tokens in, host tokens out, every step ---------------
-    engine = fresh_engine(args.batch)
-    batch_prompts = prompts(args.batch)
-    tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.warmup + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
-    output = tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.steps + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
-    e2e = {"value": round(output.metrics.decode_tokens_per_second, 1), "unit": "tok/s",
-           "h2d_bytes_per_step": layout_ints * 4, "d2h_bytes_per_step": 2 * args.batch * 4,
-           "steps": output.metrics.decode_steps}
+    e2e = None
+    if "e2e" in sections:
+        engine = fresh_engine(args.batch)
+        batch_prompts = prompts(args.batch)
+        tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.warmup + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
+        output = tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.steps + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
+        e2e = {"value": round(output.metrics.decode_tokens_per_second, 1), "unit": "tok/s",
+               "h2d_bytes_per_step": layout_ints * 4, "d2h_bytes_per_step": 2 * args.batch * 4,
+               "steps": output.metrics.decode_steps}
 
     record = {
         "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,

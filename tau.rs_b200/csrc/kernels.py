@@ -180,6 +180,33 @@ def gemm_skinny(values, weight, bias, out) -> None:
                                    ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), _stream()), "gemm_skinny")
 
 
+def _tc_fits(values, weight, out) -> bool:
+    return (values.dtype == torch.bfloat16 and values.shape[1] % 8 == 0 and values.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+            and values.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_tc(values, weight, bias, out, token_box: int = 0) -> None:
+    """bfloat16 product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); any M and N, K % 8 == 0."""
+    _on_device(values, weight, bias, out)
+    rows, depth = values.shape
+    features = weight.shape[0]
+    _require(weight.shape[1] == depth and out.shape == (rows, features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(values.dtype == weight.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32),
+             "inputs must be bfloat16 and the output bfloat16 or float32")
+    _require(_tc_fits(values, weight, out), "needs K % 8 == 0 and 16-byte aligned rows")
+    _f32_vector(bias, features, "the bias")
+    library = build.load_library("gemm_tc.cu")
+    _check(library.tau_gemm_tc(_code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out), ctypes.c_int(rows),
+                               ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
+                               ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box), _stream()),
+           "gemm_tc")
+
+
+def gemm_tc_status() -> int:
+    """0 unless a bounded wait inside the tensor-core product ran out (synchronises the device)."""
+    return build.load_library("gemm_tc.cu").tau_gemm_tc_status()
+
+
 def gemm_library(values, weight, bias, out) -> None:
     """bfloat16 product through the vendor library (cuBLAS by way of torch), as the reference's engine does for
     its dense projections (crates/models/src/components/cuda/decode/operation.rs:150-193)."""
@@ -195,8 +222,8 @@ def linear(values, weight, bias, out) -> None:
     if values.dtype == torch.bfloat16:
         if _skinny_fits(values, weight, out):
             return gemm_skinny(values, weight, bias, out)
-        if out.dtype == torch.bfloat16 and values.shape[0] > SKINNY_MAX_ROWS:
-            return gemm_library(values, weight, bias, out)
+        if _tc_fits(values, weight, out):
+            return gemm_tc(values, weight, bias, out)
     gemm_simt(values, weight, bias, out)
 
 

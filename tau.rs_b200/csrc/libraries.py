@@ -9,6 +9,7 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("elementwise.cu", ()),
         ("gemm_simt.cu", ()),
         ("gemm_skinny.cu", ()),
+        ("gemm_tc.cu", ()),
         ("attention_generic.cu", ()),
         ("sampling.cu", ()),
         # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.

@@ -106,6 +106,24 @@ def test_gemm_skinny(out_dtype, m, n, k):
         close(found, wanted, out_dtype)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k,box", [(1, 8, 8, 0), (16, 128, 64, 0), (33, 130, 72, 0), (128, 128, 128, 0), (200, 300, 200, 0),
+                                       (257, 129, 520, 0), (700, 260, 1032, 0), (40, 500, 96, 16), (100, 257, 136, 32),
+                                       (300, 100, 64, 128), (64, 1000, 224, 256)])
+def test_gemm_tc(out_dtype, m, n, k, box):
+    """The tcgen05 product at ragged sizes (zero-filled tails in every direction), every token tile, strided views."""
+    values = randn(m, k + 8, dtype=torch.bfloat16, seed=18)[:, :k]
+    weight = randn(n + 3, k, dtype=torch.bfloat16, seed=19)[:n]
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(20)).to(DEVICE)
+    for use_bias in (None, bias):
+        found = torch.full((m, n + 5), float("nan"), dtype=out_dtype, device=DEVICE)[:, :n]
+        wanted = torch.empty(m, n, dtype=out_dtype)
+        kernels.gemm_tc(values, weight, use_bias, found, box)
+        plain_kernels.linear(values.cpu(), weight.cpu(), None if use_bias is None else use_bias.cpu(), wanted)
+        close(found, wanted, out_dtype)
+    assert kernels.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_dispatch_matches_plain(dtype):
     """Whatever kernel `linear` picks for a shape, the product is the same: ragged and aligned shapes, views of a stack."""
