@@ -225,6 +225,215 @@ decode_partial_kernel(const T* __restrict__ queries, const T* __restrict__ keys,
     }
 }
 
+#if TAU_DTYPE == 1
+// ---- bfloat16: the same split on the tensor cores ----------------------------------------------------------
+// A warp takes blocks of 16 keys.  Scores are mma.sync m16n8k16 products with the group's query heads as the
+// rows of A (rows beyond the group are zero) and the keys as the columns of B; a thread's 16-byte load of a key
+// row (8 consecutive elements) feeds two products, which permutes the head dimension inside a chunk of 32
+// identically for queries and keys.  Probabilities stay in registers: the C fragments of two key tiles are
+// the A fragment of the second product, whose B fragments are built from 16-byte loads of value rows (one key,
+// 8 consecutive columns per load) with byte permutes; output column `64 r + 8 n + j` sits in column slot `n` of
+// tile `j` of round `r`, so a thread ends up owning 16 consecutive columns of each round.
+constexpr int kQkChunks = (D + 31) / 32;   // chunks of 32 head elements for the score products
+constexpr int kRounds = (D + 63) / 64;     // rounds of 64 output columns
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const unsigned*>(&pair);
+}
+
+template <int GH>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restrict__ keys, const bf16* __restrict__ values,
+                          bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                          const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
+                          int n_heads, int n_kv_heads, int passes, float scale, int window, int splits) {
+    __shared__ float merge_o[kWarps][GH][D];
+    __shared__ float merge_ml[kWarps][GH][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, seq = blockIdx.z;
+    const int kv_head = blockIdx.y / passes, pass = blockIdx.y % passes;
+    const int group = n_heads / n_kv_heads;
+    const int head0 = kv_head * group + pass * GH;
+    const int heads_here = min(GH, group - pass * GH);
+    const int length = seq_len[seq];
+    const int first = (window > 0 && length > window) ? length - window : 0;
+    const int span = length - first;
+    const int per_split = ((span + splits - 1) / splits + 31) / 32 * 32;
+    const int lo = first + split * per_split;
+    const int hi = min(length, lo + per_split);
+    const size_t record = (static_cast<size_t>(seq) * n_heads + head0) * splits + split;
+
+    if (lo >= hi) {
+        if (splits > 1 && threadIdx.x < heads_here) {
+            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2] = -INFINITY;
+            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2 + 1] = 0.0f;
+        }
+        return;
+    }
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    // Query fragments: head g of this pass, elements 32 c + 8 t .. + 8 of chunk c.
+    uint4 q_frag[kQkChunks];
+    {
+        const bool head_live = g < heads_here;
+        const bf16* q_row = queries + (static_cast<size_t>(seq) * n_heads + head0 + (head_live ? g : 0)) * D;
+#pragma unroll
+        for (int c = 0; c < kQkChunks; ++c) {
+            const int e = 32 * c + 8 * t;
+            q_frag[c] = (head_live && e + 8 <= D) ? *reinterpret_cast<const uint4*>(q_row + e) : zero4;
+        }
+    }
+    const int* pages = page_rows + static_cast<size_t>(seq) * page_stride;
+    const size_t head_stride = static_cast<size_t>(page_tokens) * D;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    float running_max = -INFINITY, running_sum = 0.0f;   // of row g, in units of log2; the sum is this thread's share
+    float acc[kRounds][8][4];
+#pragma unroll
+    for (int r = 0; r < kRounds; ++r)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.0f;
+
+    auto row_offset = [&](int key) {   // a key beyond the range is replaced by the last one; its probability is zero
+        const int k = min(key, hi - 1);
+        return (static_cast<size_t>(pages[k / page_tokens]) * n_kv_heads + kv_head) * head_stride + static_cast<size_t>(k % page_tokens) * D;
+    };
+
+    for (int base = lo + warp * 16; base < hi; base += kWarps * 16) {
+        // Loads first: key rows base + 8 nt + g, value rows base + {2t, 2t+1, 2t+8, 2t+9}.
+        uint4 k_frag[2][kQkChunks];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const bf16* key_row = keys + row_offset(base + 8 * nt + g);
+#pragma unroll
+            for (int c = 0; c < kQkChunks; ++c) {
+                const int e = 32 * c + 8 * t;
+                k_frag[nt][c] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(key_row + e) : zero4;
+            }
+        }
+        uint4 v_frag[kRounds][4];
+        {
+            const int slots[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const bf16* value_row = values + row_offset(base + slots[s]);
+#pragma unroll
+                for (int r = 0; r < kRounds; ++r) {
+                    const int e = 64 * r + 8 * g;
+                    v_frag[r][s] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(value_row + e) : zero4;
+                }
+            }
+        }
+        // Scores of 16 keys: two tiles of 8.
+        float score[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) score[nt][i] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < kQkChunks; ++c) {
+                mma_bf16(score[nt], q_frag[c].x, 0u, q_frag[c].y, 0u, k_frag[nt][c].x, k_frag[nt][c].y);
+                mma_bf16(score[nt], q_frag[c].z, 0u, q_frag[c].w, 0u, k_frag[nt][c].z, k_frag[nt][c].w);
+            }
+        }
+        // Row g holds keys base + 8 nt + 2t + {0, 1} in score[nt][0..1].
+        float block_max = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = base + 8 * nt + 2 * t + e;
+                score[nt][e] = key < hi ? score[nt][e] * scale_log2 : -INFINITY;
+                block_max = fmaxf(block_max, score[nt][e]);
+            }
+        block_max = fmaxf(block_max, __shfl_xor_sync(0xffffffffu, block_max, 1));
+        block_max = fmaxf(block_max, __shfl_xor_sync(0xffffffffu, block_max, 2));
+        const float new_max = fmaxf(running_max, block_max);     // finite: key `base` is inside the range
+        const float correction = exp2f(running_max - new_max);
+        running_max = new_max;
+        float p[2][2];
+        float block_sum_share = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p[nt][e] = exp2f(score[nt][e] - new_max);
+                block_sum_share += p[nt][e];
+            }
+        running_sum = running_sum * correction + block_sum_share;
+        const unsigned pa0 = pack_bf16(p[0][0], p[0][1]), pa2 = pack_bf16(p[1][0], p[1][1]);
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const unsigned* k0 = reinterpret_cast<const unsigned*>(&v_frag[r][0]);   // key 2t
+            const unsigned* k1 = reinterpret_cast<const unsigned*>(&v_frag[r][1]);   // key 2t + 1
+            const unsigned* k8 = reinterpret_cast<const unsigned*>(&v_frag[r][2]);   // key 2t + 8
+            const unsigned* k9 = reinterpret_cast<const unsigned*>(&v_frag[r][3]);   // key 2t + 9
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                // Column j of each row is halfword j of its vector: word j / 2, low or high half.
+                const unsigned selector = (j & 1) ? 0x7632u : 0x5410u;
+                const unsigned b0 = __byte_perm(k0[j >> 1], k1[j >> 1], selector);
+                const unsigned b1 = __byte_perm(k8[j >> 1], k9[j >> 1], selector);
+                acc[r][j][0] *= correction;
+                acc[r][j][1] *= correction;
+                mma_bf16(acc[r][j], pa0, 0u, pa2, 0u, b0, b1);
+            }
+        }
+    }
+    // This warp's row g: the sum over the four threads of the row; columns 64 r + 16 t + j (c0) and + 8 (c1).
+    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
+    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
+    if (g < GH) {
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c0 = 64 * r + 16 * t + j, c1 = c0 + 8;
+                if (c0 < D) merge_o[warp][g][c0] = acc[r][j][0];
+                if (c1 < D) merge_o[warp][g][c1] = acc[r][j][1];
+            }
+        if (t == 0) {
+            merge_ml[warp][g][0] = running_max;
+            merge_ml[warp][g][1] = running_sum;
+        }
+    }
+    __syncthreads();
+    for (int index = threadIdx.x; index < heads_here * D; index += kWarps * 32) {
+        const int h = index / D, c = index % D;
+        float total_max = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) total_max = fmaxf(total_max, merge_ml[w][h][0]);
+        float o = 0.0f, sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float factor = exp2f(merge_ml[w][h][0] - total_max);   // 0 for a warp that saw no key
+            if (factor > 0.0f) {
+                o += merge_o[w][h][c] * factor;
+                sum += merge_ml[w][h][1] * factor;
+            }
+        }
+        if (splits == 1) {
+            out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
+        } else {
+            const size_t slot = record + static_cast<size_t>(h) * splits;
+            partial_o[slot * D + c] = o;
+            if (c == 0) {
+                partial_ml[slot * 2] = total_max * 0.6931471805599453f;   // records are kept in natural-log units
+                partial_ml[slot * 2 + 1] = sum;
+            }
+        }
+    }
+}
+#endif  // TAU_DTYPE == 1
+
 __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       T* __restrict__ out, int n_heads, int splits) {
     const int head = blockIdx.x, seq = blockIdx.y;
@@ -268,8 +477,13 @@ TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const
     const dim3 grid(splits, n_kv_heads * passes, n_seqs);
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + static_cast<size_t>(n_seqs) * n_heads * splits * D : nullptr;
+#if TAU_DTYPE == 1
+#define TAU_KERNEL decode_partial_mma_kernel
+#else
+#define TAU_KERNEL decode_partial_kernel
+#endif
 #define TAU_LAUNCH(GH)                                                                                                          \
-    decode_partial_kernel<GH><<<grid, kWarps * 32, 0, s>>>(static_cast<const T*>(queries), static_cast<const T*>(keys),          \
+    TAU_KERNEL<GH><<<grid, kWarps * 32, 0, s>>>(static_cast<const T*>(queries), static_cast<const T*>(keys),          \
                                                           static_cast<const T*>(values), static_cast<T*>(out), partial_o, partial_ml, \
                                                           seq_len, page_rows, page_stride, page_tokens, n_heads, n_kv_heads, passes,   \
                                                           scale, window, splits)
@@ -278,6 +492,7 @@ TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const
     else if (gh == 4) TAU_LAUNCH(4);
     else TAU_LAUNCH(8);
 #undef TAU_LAUNCH
+#undef TAU_KERNEL
     int status = tau_launch_status();
     if (status || splits == 1) return status;
     decode_combine_kernel<<<dim3(n_heads, n_seqs), D < 128 ? D : 128, 0, s>>>(partial_o, partial_ml, static_cast<T*>(out), n_heads, splits);

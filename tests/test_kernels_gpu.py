@@ -221,6 +221,30 @@ def test_attention_over_pages(dtype, n_heads, n_kv_heads, head_dim, window):
     close(found, wanted, dtype)
 
 
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [
+    (4, 4, 16, 0), (6, 2, 48, 0), (8, 2, 128, 0), (10, 2, 64, 0), (3, 1, 256, 0), (2, 1, 80, 0), (8, 2, 128, 50), (4, 2, 32, 16)])
+def test_prefill_attention_kernel(n_heads, n_kv_heads, head_dim, window):
+    """The tensor-core prefill kernel on whole prompts, continued runs, ragged tiles and a window's edge."""
+    dtype = torch.bfloat16
+    lengths, new_counts = [70, 200, 129, 1, 64, 333], [70, 17, 129, 1, 33, 100]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=70, pages=48)
+    tokens = positions.shape[0]
+    queries = randn(tokens, n_heads * head_dim, dtype=dtype, seed=71)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new_counts)]), dtype=torch.int32, device=DEVICE)
+    starts = torch.tensor([l - n for l, n in zip(lengths, new_counts)], dtype=torch.int32, device=DEVICE)
+    # Poison what lies beyond each sequence's length: nothing there may be read into a result.
+    for index, length in enumerate(lengths):
+        for place in range(length, ((length + 63) // 64) * 64):
+            keys[int(rows[index, place // 64]), :, place % 64] = float("nan")
+            values[int(rows[index, place // 64]), :, place % 64] = float("nan")
+    found = torch.full_like(queries, float("nan"))
+    wanted = torch.empty(tokens, n_heads * head_dim, dtype=dtype)
+    kernels.attention_prefill(queries, keys, values, found, cu, starts, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
+    close(found, wanted, dtype)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim", [(4, 2, 16), (8, 2, 128), (6, 1, 80)])
 def test_decode_attention_finds_a_far_key(dtype, n_heads, n_kv_heads, head_dim):
