@@ -90,6 +90,8 @@ decode_partial_kernel(const T* __restrict__ queries, const T* __restrict__ keys,
                       T* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
                       const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
                       int n_heads, int n_kv_heads, int passes, float scale, int window, int splits) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     __shared__ __align__(16) float q_shared[GH][D];
     __shared__ float merge_o[kWarps][GH][D];
     __shared__ float merge_ml[kWarps][GH][2];
@@ -254,6 +256,8 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
                           bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
                           const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
                           int n_heads, int n_kv_heads, int passes, float scale, int window, int splits) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     __shared__ float merge_o[kWarps][GH][D];
     __shared__ float merge_ml[kWarps][GH][2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -307,9 +311,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
         return (static_cast<size_t>(pages[k / page_tokens]) * n_kv_heads + kv_head) * head_stride + static_cast<size_t>(k % page_tokens) * D;
     };
 
-    for (int base = lo + warp * 16; base < hi; base += kWarps * 16) {
-        // Loads first: key rows base + 8 nt + g, value rows base + {2t, 2t+1, 2t+8, 2t+9}.
-        uint4 k_frag[2][kQkChunks];
+    auto load_keys = [&](int base, uint4 (&k_frag)[2][kQkChunks]) {   // key rows base + 8 nt + g
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const bf16* key_row = keys + row_offset(base + 8 * nt + g);
@@ -319,6 +321,12 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
                 k_frag[nt][c] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(key_row + e) : zero4;
             }
         }
+    };
+    // Software pipeline: the values of a block are requested before its scores are computed, and the keys of
+    // the next block right after, so each load has a product and a softmax to arrive behind.
+    uint4 k_frag[2][kQkChunks];
+    if (lo + warp * 16 < hi) load_keys(lo + warp * 16, k_frag);
+    for (int base = lo + warp * 16; base < hi; base += kWarps * 16) {
         uint4 v_frag[kRounds][4];
         {
             const int slots[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
@@ -344,6 +352,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
                 mma_bf16(score[nt], q_frag[c].z, 0u, q_frag[c].w, 0u, k_frag[nt][c].z, k_frag[nt][c].w);
             }
         }
+        if (base + kWarps * 16 < hi) load_keys(base + kWarps * 16, k_frag);
         // Row g holds keys base + 8 nt + 2t + {0, 1} in score[nt][0..1].
         float block_max = -INFINITY;
 #pragma unroll
@@ -436,6 +445,8 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
 
 __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       T* __restrict__ out, int n_heads, int splits) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int head = blockIdx.x, seq = blockIdx.y;
     const size_t base = (static_cast<size_t>(seq) * n_heads + head) * splits;
     float total_max = -INFINITY;
@@ -483,7 +494,7 @@ TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const
 #define TAU_KERNEL decode_partial_kernel
 #endif
 #define TAU_LAUNCH(GH)                                                                                                          \
-    TAU_KERNEL<GH><<<grid, kWarps * 32, 0, s>>>(static_cast<const T*>(queries), static_cast<const T*>(keys),          \
+    tau_launch(TAU_KERNEL<GH>, dim3(grid), dim3(kWarps * 32), 0, s, static_cast<const T*>(queries), static_cast<const T*>(keys),          \
                                                           static_cast<const T*>(values), static_cast<T*>(out), partial_o, partial_ml, \
                                                           seq_len, page_rows, page_stride, page_tokens, n_heads, n_kv_heads, passes,   \
                                                           scale, window, splits)
@@ -495,6 +506,6 @@ TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const
 #undef TAU_KERNEL
     int status = tau_launch_status();
     if (status || splits == 1) return status;
-    decode_combine_kernel<<<dim3(n_heads, n_seqs), D < 128 ? D : 128, 0, s>>>(partial_o, partial_ml, static_cast<T*>(out), n_heads, splits);
+    tau_launch(decode_combine_kernel, dim3(n_heads, n_seqs), dim3(D < 128 ? D : 128), 0, s, partial_o, partial_ml, static_cast<T*>(out), n_heads, splits);
     return tau_launch_status();
 }

@@ -21,6 +21,8 @@ __global__ void attention_prepare_kernel(
     const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
     int page_stride, int page_tokens, int n_heads, int n_kv_heads, int head_dim, int write_cache) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int token = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int position = positions[token];
@@ -89,6 +91,8 @@ __global__ void attention_generic_kernel(
     const T* __restrict__ queries, const T* __restrict__ keys, const T* __restrict__ values, T* __restrict__ out,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
     int page_stride, int page_tokens, int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale, int window) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     extern __shared__ float query_shared[];  // [warps][head_dim]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const long long pair = static_cast<long long>(blockIdx.x) * warps + warp;
@@ -169,12 +173,12 @@ TAU_EXPORT int tau_attention_prepare(
     const int heads_total = write_cache ? n_heads + 2 * n_kv_heads : n_heads;
     const int threads = 32 * (heads_total < 8 ? heads_total : 8);
     if (dtype == TAU_F32)
-        attention_prepare_kernel<float><<<n_tokens, threads, 0, s>>>(
+        tau_launch(attention_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 
             static_cast<const float*>(projected), projected_stride, static_cast<float*>(queries), static_cast<float*>(keys),
             static_cast<float*>(values), q_weight, k_weight, eps, cos_table, sin_table, rotary_dim, positions, token_seq,
             page_rows, page_stride, page_tokens, n_heads, n_kv_heads, head_dim, write_cache);
     else if (dtype == TAU_BF16)
-        attention_prepare_kernel<bf16><<<n_tokens, threads, 0, s>>>(
+        tau_launch(attention_prepare_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, 
             static_cast<const bf16*>(projected), projected_stride, static_cast<bf16*>(queries), static_cast<bf16*>(keys),
             static_cast<bf16*>(values), q_weight, k_weight, eps, cos_table, sin_table, rotary_dim, positions, token_seq,
             page_rows, page_stride, page_tokens, n_heads, n_kv_heads, head_dim, write_cache);
@@ -198,12 +202,12 @@ TAU_EXPORT int tau_attention_generic(
     const unsigned blocks = static_cast<unsigned>((pairs + warps - 1) / warps);
     const size_t shared = warps * head_dim * sizeof(float);
     if (dtype == TAU_F32)
-        attention_generic_kernel<float><<<blocks, warps * 32, shared, s>>>(
+        tau_launch(attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), shared, s, 
             static_cast<const float*>(queries), static_cast<const float*>(keys), static_cast<const float*>(values),
             static_cast<float*>(out), positions, token_seq, page_rows, page_stride, page_tokens, n_tokens, n_heads,
             n_kv_heads, head_dim, scale, window);
     else if (dtype == TAU_BF16)
-        attention_generic_kernel<bf16><<<blocks, warps * 32, shared, s>>>(
+        tau_launch(attention_generic_kernel<bf16>, dim3(blocks), dim3(warps * 32), shared, s, 
             static_cast<const bf16*>(queries), static_cast<const bf16*>(keys), static_cast<const bf16*>(values),
             static_cast<bf16*>(out), positions, token_seq, page_rows, page_stride, page_tokens, n_tokens, n_heads,
             n_kv_heads, head_dim, scale, window);

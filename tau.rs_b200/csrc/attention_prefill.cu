@@ -49,18 +49,22 @@ attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restric
                          bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ page_rows, int page_stride, int page_tokens, int n_seqs, int n_heads, int n_kv_heads,
                          int heads_per_block, int passes, float scale, int window) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int tiles_per_block = kWarps / heads_per_block;
     const int group = n_heads / n_kv_heads;
-    // Which sequence does this block belong to?  Blocks are numbered sequence by sequence, longest tiles last in
-    // each; a block index beyond the last sequence has nothing to do.
+    // Which sequence does this block belong to?  Blocks are numbered sequence by sequence; a block index beyond the last sequence has nothing to do.
     int block = blockIdx.x, seq = 0, row0 = 0, n_new = 0;
     for (; seq < n_seqs; ++seq) {
         row0 = cu_seqlens[seq];
         n_new = cu_seqlens[seq + 1] - row0;
         const int blocks_here = (n_new + kTile * tiles_per_block - 1) / (kTile * tiles_per_block);
-        if (block < blocks_here) break;
+        if (block < blocks_here) {
+            block = blocks_here - 1 - block;   // the last tiles have the most keys: they start first
+            break;
+        }
         block -= blocks_here;
     }
     if (seq >= n_seqs) return;
@@ -109,8 +113,7 @@ attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restric
     int first_key = 0;
     if (window > 0 && position0 - window + 1 > 0) first_key = (position0 - window + 1) & ~15;   // the earliest key of row 0, on a block boundary
 
-    for (int base = first_key; base <= last_position; base += 16) {
-        uint4 k_frag[2][kQkChunks];
+    auto load_keys = [&](int base, uint4 (&k_frag)[2][kQkChunks]) {   // key rows base + 8 nt + g
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             const bf16* key_row = keys + row_offset(base + 8 * nt + g);
@@ -120,6 +123,12 @@ attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restric
                 k_frag[nt][c] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(key_row + e) : zero4;
             }
         }
+    };
+    // Software pipeline: the values of a block are requested before its scores are computed, and the keys of
+    // the next block right after, so each load has a product and a softmax to arrive behind.
+    uint4 k_frag[2][kQkChunks];
+    load_keys(first_key, k_frag);
+    for (int base = first_key; base <= last_position; base += 16) {
         uint4 v_frag[kRounds][4];
         {
             const int slots[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
@@ -144,6 +153,7 @@ attention_prefill_kernel(const bf16* __restrict__ queries, const bf16* __restric
                 mma_bf16(score[nt], q_lo[c].z, q_hi[c].z, q_lo[c].w, q_hi[c].w, k_frag[nt][c].z, k_frag[nt][c].w);
             }
         }
+        if (base + 16 <= last_position) load_keys(base + 16, k_frag);
         // score[nt][0..1]: row g, keys base + 8 nt + 2t + {0, 1}; score[nt][2..3]: row g + 8, the same keys.
         float block_lo = -INFINITY, block_hi = -INFINITY;
 #pragma unroll
@@ -245,7 +255,7 @@ TAU_EXPORT int tau_attention_prefill(const void* queries, const void* keys, cons
     const int rows_per_block = kTile * tiles_per_block;
     const int blocks = (n_tokens + rows_per_block - 1) / rows_per_block + n_seqs;   // every sequence may leave a ragged block
     const dim3 grid(blocks, n_kv_heads * passes);
-    attention_prefill_kernel<<<grid, kWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    tau_launch(attention_prefill_kernel, dim3(grid), dim3(kWarps * 32), 0, static_cast<cudaStream_t>(stream), 
         static_cast<const bf16*>(queries), static_cast<const bf16*>(keys), static_cast<const bf16*>(values), static_cast<bf16*>(out),
         cu_seqlens, seq_start, page_rows, page_stride, page_tokens, n_seqs, n_heads, n_kv_heads, heads_per_block, passes, scale, window);
     return tau_launch_status();

@@ -53,4 +53,37 @@ __device__ __forceinline__ float block_sum(float value, float* scratch) {
 
 static inline int tau_launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// Programmatic dependent launch.  Every kernel of this library starts with `grid_dependents_launch()` (the next
+// kernel in the stream may be scheduled as soon as all blocks of this one have started) and calls
+// `grid_dependency_wait()` before it reads anything an earlier kernel wrote or writes anything at all (the wait
+// returns when the previous kernel has completed and its writes are visible).  What a kernel does before the
+// wait therefore overlaps the previous kernel's tail: in the products, that is the prefetch of the weights.
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+#include <utility>
+
+static inline bool tau_dependent_launch_enabled() {
+    static const bool enabled = std::getenv("TAU_NO_DEPENDENT_LAUNCH") == nullptr;
+    return enabled;
+}
+
+// Launches `kernel` so that it may begin before the previous kernel of the stream has finished.
+template <typename... Parameters, typename... Arguments>
+static inline int tau_launch(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                             Arguments&&... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = tau_dependent_launch_enabled() ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, Parameters(std::forward<Arguments>(arguments))...));
+}
+
 TAU_EXPORT const char* tau_error_string(int code);

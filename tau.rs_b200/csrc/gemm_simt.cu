@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(kThreads)
 gemm_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const float* __restrict__ bias,
                  TOut* __restrict__ out, int M, int N, int K, long long x_stride, long long w_stride,
                  long long out_stride) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     __shared__ float xs[kDepth][kTile + 4];
     __shared__ float ws[kDepth][kTile + 4];
     const int row0 = blockIdx.y * kTile, col0 = blockIdx.x * kTile;
@@ -66,7 +68,7 @@ template <typename TIn, typename TOut>
 int launch(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride,
            long long w_stride, long long out_stride, cudaStream_t stream) {
     dim3 grid((N + kTile - 1) / kTile, (M + kTile - 1) / kTile);
-    gemm_simt_kernel<TIn, TOut><<<grid, kThreads, 0, stream>>>(static_cast<const TIn*>(x), static_cast<const TIn*>(w), bias,
+    tau_launch(gemm_simt_kernel<TIn, TOut>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const TIn*>(x), static_cast<const TIn*>(w), bias,
                                                               static_cast<TOut*>(out), M, N, K, x_stride, w_stride, out_stride);
     return tau_launch_status();
 }

@@ -29,10 +29,17 @@ template <int NB, typename TOut>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias, TOut* __restrict__ out,
                    int M, int N, int K, long long x_stride, long long w_stride, long long out_stride) {
+    grid_dependents_launch();
     __shared__ float partial[kWarps][NB * 8][kRows + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * kRows;
+    // The weights do not depend on the previous kernel: ask L2 for this block's rows, then wait for the activations.
+    if (threadIdx.x < kRows && row0 + threadIdx.x < N) {
+        const bf16* row = w + static_cast<size_t>(row0 + threadIdx.x) * w_stride;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(static_cast<unsigned>(K) * 2u) : "memory");
+    }
+    grid_dependency_wait();
     // Rows beyond N are clamped for loading and dropped when storing.
     const bf16* w_lo = w + static_cast<size_t>(min(row0 + g, N - 1)) * w_stride;
     const bf16* w_hi = w + static_cast<size_t>(min(row0 + g + 8, N - 1)) * w_stride;
@@ -95,10 +102,10 @@ int launch(int out_dtype, const void* x, const void* w, const float* bias, void*
            long long w_stride, long long out_stride, cudaStream_t stream) {
     const unsigned blocks = (N + kRows - 1) / kRows;
     if (out_dtype == TAU_BF16)
-        gemm_skinny_kernel<NB, bf16><<<blocks, kWarps * 32, 0, stream>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, bf16>, dim3(blocks), dim3(kWarps * 32), 0, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                         static_cast<bf16*>(out), M, N, K, x_stride, w_stride, out_stride);
     else
-        gemm_skinny_kernel<NB, float><<<blocks, kWarps * 32, 0, stream>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, float>, dim3(blocks), dim3(kWarps * 32), 0, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                          static_cast<float*>(out), M, N, K, x_stride, w_stride, out_stride);
     return tau_launch_status();
 }

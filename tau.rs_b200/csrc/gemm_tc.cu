@@ -141,6 +141,7 @@ template <int BN, typename TOut>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
                const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
+    grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
@@ -175,6 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     __syncthreads();
     tensor_fence_after_sync();
     const uint32_t tensor_base = shared->tensor_memory_base;
+    grid_dependency_wait();   // barriers and tensor memory were set up while the previous kernel was finishing
 
     if (warp == 0) {
         // ---- producer: TMA loads of the weight and input tiles of each stage --------------------------
@@ -316,7 +318,7 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
     }
     const int tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
     const int blocks = tiles < sm_count() ? tiles : sm_count();
-    gemm_tc_kernel<BN, TOut><<<blocks, kThreads, shared_bytes, stream>>>(weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
+    tau_launch(gemm_tc_kernel<BN, TOut>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
                                                                          out_stride, stages);
     return tau_launch_status();
 }

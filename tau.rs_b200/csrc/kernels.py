@@ -281,14 +281,16 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
         ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention")
 
 
-def decode_splits(n_seqs: int, max_len: int) -> int:
+def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     """Number of context splits that decode attention uses for this many sequences of at most this length.
 
-    The length is rounded up to a power of two first, so that a captured graph (whose key holds this
-    number) serves a whole range of lengths; a split covers at least 128 positions.
+    `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  The aim is about
+    four blocks per SM in all, each split at least 64 positions long.  The length is rounded up to a power of two
+    first, so that a captured graph (whose key holds this number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
-    return max(1, min(bucket // 128, 1024 // max(1, n_seqs), 64))
+    wanted = -(-592 // max(1, n_seqs * kv_blocks))
+    return max(1, min(wanted, bucket // 64, 64))
 
 
 _decode_scratch = {}

@@ -79,6 +79,8 @@ template <bool Gumbel>
 __global__ void chunk_best_kernel(const float* __restrict__ logits, unsigned vocab, unsigned* __restrict__ scratch,
                                   float inverse_temperature, unsigned seed_lo, unsigned seed_hi,
                                   const int* __restrict__ request_ids, const int* __restrict__ token_indices) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     __shared__ Candidate partial[kThreads / 32];
     const unsigned row = blockIdx.y;
     const float* row_logits = logits + static_cast<size_t>(row) * vocab;
@@ -106,6 +108,8 @@ __global__ void chunk_best_kernel(const float* __restrict__ logits, unsigned voc
 
 __global__ void merge_best_kernel(const unsigned* __restrict__ scratch, unsigned chunks, int* __restrict__ tokens,
                                   int* __restrict__ valid) {
+    grid_dependents_launch();
+    grid_dependency_wait();
     __shared__ Candidate partial[kThreads / 32];
     const unsigned row = blockIdx.x;
     const unsigned* row_scratch = scratch + static_cast<size_t>(row) * chunks * 3;
@@ -136,10 +140,10 @@ TAU_EXPORT int tau_argmax(const float* logits, int rows, int vocab, unsigned* sc
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
-    chunk_best_kernel<false><<<dim3(chunks, rows), kThreads, 0, s>>>(logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
+    tau_launch(chunk_best_kernel<false>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
     int status = tau_launch_status();
     if (status) return status;
-    merge_best_kernel<<<rows, kThreads, 0, s>>>(scratch, chunks, tokens, valid);
+    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
     return tau_launch_status();
 }
 
@@ -152,12 +156,12 @@ TAU_EXPORT int tau_sample_gumbel(const float* logits, int rows, int vocab, unsig
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
-    chunk_best_kernel<true><<<dim3(chunks, rows), kThreads, 0, s>>>(logits, vocab, scratch, inverse_temperature,
+    tau_launch(chunk_best_kernel<true>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, inverse_temperature,
                                                                    static_cast<unsigned>(seed), static_cast<unsigned>(seed >> 32),
                                                                    request_ids, token_indices);
     int status = tau_launch_status();
     if (status) return status;
-    merge_best_kernel<<<rows, kThreads, 0, s>>>(scratch, chunks, tokens, valid);
+    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
     return tau_launch_status();
 }
 
@@ -205,9 +209,9 @@ TAU_EXPORT int tau_argmax_static(const float* logits, int rows, int vocab, int* 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
     // Writes scratch[0 .. rows * chunks * 3): every word that the merge below reads.
-    chunk_best_kernel<false><<<dim3(chunks, rows), kThreads, 0, s>>>(logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
+    tau_launch(chunk_best_kernel<false>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
     int launched = tau_launch_status();
     if (launched) return launched;
-    merge_best_kernel<<<rows, kThreads, 0, s>>>(scratch, chunks, tokens, valid);
+    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
     return tau_launch_status();
 }

@@ -31,7 +31,7 @@ class _DecodeGraph:
 
 def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]):
     max_len = max(start + 1 for start in starts)
-    splits = kernels.decode_splits(len(entries), max_len)
+    splits = engine.model.decode_splits(len(entries), max_len)
     key = (len(entries), splits)
     state = engine._graphs.get(key)
     if state is None:

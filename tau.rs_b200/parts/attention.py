@@ -52,6 +52,12 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed("kv", n_kv_heads=self.spec.n_kv_heads, head_dim=self.spec.head_dim, window=self.spec.window)
 
+    def decode_blocks(self) -> int:
+        """Blocks that the decode kernel launches per sequence and context split."""
+        group = self.spec.n_heads // self.spec.n_kv_heads
+        heads_per_pass = 8 if group >= 8 else 4 if group > 2 else group
+        return self.spec.n_kv_heads * -(-group // heads_per_pass)
+
     def tensor_specs(self):
         specs = {}
         for part in self._children:

@@ -112,6 +112,12 @@ class DecoderModel:
                 total += count * torch.empty((), dtype=device_dtype(spec, self.dtype)).element_size()
         return total + self.spec.vocab_size * self.spec.hidden * torch.empty((), dtype=self.dtype).element_size()
 
+    def decode_splits(self, n_seqs: int, max_len: int) -> int:
+        """Context splits for a decode step of `n_seqs` sequences (part of a captured graph's key)."""
+        blocks = [block.mixer.decode_blocks() for block in self.blocks
+                  if hasattr(block, "mixer") and hasattr(block.mixer, "decode_blocks")]
+        return kernels.decode_splits(n_seqs, max_len, min(blocks) if blocks else 1)
+
     # ---- forward -----------------------------------------------------------------
     def forward(self, step, cache) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns 32-bit logits `[wanted, vocab]`, or None if nothing is wanted."""

@@ -107,7 +107,7 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
     out.copy_(result.view(tokens, n_heads * head_dim).to(out.dtype))
 
 
-def decode_splits(n_seqs, max_len):
+def decode_splits(n_seqs, max_len, kv_blocks=8):
     return 1
 
 

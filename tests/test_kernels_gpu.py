@@ -35,7 +35,7 @@ def test_embedding(dtype, width, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,width,eps", [(1, 16, 1e-6), (5, 97, 1e-5), (3, 1000, 1e-3), (2, 4100, 1e-6)])
+@pytest.mark.parametrize("rows,width,eps", [(1, 16, 1e-6), (5, 97, 1e-5), (3, 1000, 1e-3), (2, 4100, 1e-6), (9, 4096, 1e-6), (2, 8192, 1e-5), (2, 12288, 1e-6)])
 def test_rms_norm(dtype, rows, width, eps):
     values = randn(rows, width, dtype=dtype, seed=2, scale=3.0)
     branch = randn(rows, width, dtype=dtype, seed=3)
@@ -54,7 +54,7 @@ def test_rms_norm(dtype, rows, width, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,width", [(1, 64), (4, 97), (3, 2050)])
+@pytest.mark.parametrize("rows,width", [(1, 64), (4, 97), (3, 2050), (8, 4096), (70, 1024), (2, 5120), (2, 9000)])
 def test_add_rms_norm(dtype, rows, width):
     branch = randn(rows, width, dtype=dtype, seed=5)
     residual = randn(rows, width, dtype=dtype, seed=6, scale=2.0)
@@ -68,7 +68,7 @@ def test_add_rms_norm(dtype, rows, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,width", [(1, 1), (3, 225), (70, 1000)])
+@pytest.mark.parametrize("rows,width", [(1, 1), (3, 225), (70, 1000), (8, 12288), (33, 72)])
 def test_silu_mul(dtype, rows, width):
     stacked = randn(rows, 2 * width, dtype=dtype, seed=8, scale=4.0)
     found = torch.empty(rows, width, dtype=dtype, device=DEVICE)
