@@ -205,12 +205,15 @@ def main() -> int:
         torch.cuda.empty_cache()
         return elapsed, launches, record, live_bytes, layout_ints
 
-    elapsed, launches, clocks, live_bytes, layout_ints = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
-    ms_per_step = elapsed / args.steps
-    value = args.batch * args.steps / (elapsed * 1e-3)
-    achieved = (weight_bytes + live_bytes) / (ms_per_step * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
+    value = ms_per_step = launches = clocks = roofline = None
+    live_bytes = layout_ints = 0
+    if "decode" in sections:
+        elapsed, launches, clocks, live_bytes, layout_ints = decode_run(args.batch, args.steps, args.warmup, sample_clocks=True)
+        ms_per_step = round(elapsed / args.steps, 4)
+        value = round(args.batch * args.steps / (elapsed * 1e-3), 1)
+        achieved = (weight_bytes + live_bytes) / (elapsed / args.steps * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(achieved / peaks["hbm_gbs"], 4), "of": peaks["source"]}
 
     points = {}
     if "points" in sections:
@@ -230,8 +233,8 @@ def main() -> int:
                "steps": output.metrics.decode_steps}
 
     record = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)", "impl": "ours",
         "config": {
             "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": config["hidden_size"],
