@@ -2,12 +2,13 @@
 //
 // The reference runs these products through cuBLAS as m x 1 x k problems (crates/models/src/components/cuda/
 // decode/operation.rs:150-193).  Here the step is bound by reading `w` once from HBM, so the kernel is shaped
-// around that stream: a block owns 16 consecutive output features, its 8 warps split K in interleaved chunks of
-// 64 elements, every thread keeps several 16-byte weight loads in flight, and the few activation rows are
-// re-read from L1/L2.  The arithmetic is mma.sync m16n8k16 (bfloat16 in, float accumulate) with the weight
+// around that stream: a block owns 16 consecutive output features, its 16 warps split K in interleaved chunks of
+// 64 elements, cp.async keeps two chunks per warp in flight in lane-private shared-memory slots, and the few
+// activation rows are re-read from L1/L2.  (Measured on the Qwen3-8B layer shapes at 8 rows: 16 warps with two
+// chunks in flight stream 5.4 TB/s; 8 warps, deeper rings or an L2 prefetch of the block's rows are all slower.)  The arithmetic is mma.sync m16n8k16 (bfloat16 in, float accumulate) with the weight
 // rows as the A operand and the activations as B; a thread's 16-byte load is used as the fragments of two
 // consecutive MMAs, which permutes K inside a chunk identically for both operands and so leaves every dot
-// product unchanged.  Partial sums of the 8 warps meet in shared memory.
+// product unchanged.  Partial sums of the warps meet in shared memory.
 //
 // Needs K % 8 == 0, 16-byte aligned rows of x and w (row strides multiples of 8 elements); other shapes go
 // to the plain tiled kernel.
@@ -15,7 +16,16 @@
 
 namespace {
 
-constexpr int kWarps = 8;
+#ifndef TAU_SKINNY_WARPS
+#define TAU_SKINNY_WARPS 16
+#endif
+#ifndef TAU_SKINNY_PREFETCH
+#define TAU_SKINNY_PREFETCH 0
+#endif
+#ifndef TAU_SKINNY_MIN_BLOCKS
+#define TAU_SKINNY_MIN_BLOCKS 1
+#endif
+constexpr int kWarps = TAU_SKINNY_WARPS;
 constexpr int kRows = 16;       // output features per block
 constexpr int kChunk = 64;      // K elements per warp iteration
 
@@ -25,21 +35,35 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+#ifndef TAU_SKINNY_DEPTH
+#define TAU_SKINNY_DEPTH 2
+#endif
+constexpr int kDepth = TAU_SKINNY_DEPTH;                          // chunks in flight per warp
+constexpr int kRingOnlyBytes = kWarps * kDepth * 4 * 32 * 16;     // [warp][depth][piece][lane] of 16 bytes
+constexpr int kPartialBytes = kWarps * 32 * (kRows + 1) * 4;      // the largest [warp][4 * 8 tokens][17] of floats
+constexpr int kRingBytes = kRingOnlyBytes > kPartialBytes ? kRingOnlyBytes : kPartialBytes;
+
+__device__ __forceinline__ void copy_async_16(void* destination, const void* source, bool real) {
+    const unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(destination));
+    const int bytes = real ? 16 : 0;   // 0 source bytes: the 16 destination bytes become zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(address), "l"(source), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int NB, typename TOut>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, TAU_SKINNY_MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias, TOut* __restrict__ out,
                    int M, int N, int K, long long x_stride, long long w_stride, long long out_stride) {
     grid_dependents_launch();
-    __shared__ float partial[kWarps][NB * 8][kRows + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * kRows;
     // The weights do not depend on the previous kernel: ask L2 for this block's rows, then wait for the activations.
-    if (threadIdx.x < kRows && row0 + threadIdx.x < N) {
+    if (TAU_SKINNY_PREFETCH && threadIdx.x < kRows && row0 + threadIdx.x < N) {
         const bf16* row = w + static_cast<size_t>(row0 + threadIdx.x) * w_stride;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(row), "r"(static_cast<unsigned>(K) * 2u) : "memory");
     }
-    grid_dependency_wait();
     // Rows beyond N are clamped for loading and dropped when storing.
     const bf16* w_lo = w + static_cast<size_t>(min(row0 + g, N - 1)) * w_stride;
     const bf16* w_hi = w + static_cast<size_t>(min(row0 + g + 8, N - 1)) * w_stride;
@@ -58,24 +82,53 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 4
-    for (int chunk = warp * kChunk; chunk < K; chunk += kWarps * kChunk) {
+    // The weight stream goes through a ring in shared memory that is private to each lane: cp.async puts the four
+    // 16-byte pieces of a chunk into the lane's own slots `kDepth` chunks ahead, and the lane reads them back when
+    // their turn comes.  Nothing is shared between lanes, so no barrier is needed, and no register waits for data.
+    extern __shared__ __align__(16) uint8_t ring_raw[];
+    uint4* ring = reinterpret_cast<uint4*>(ring_raw) + (static_cast<size_t>(warp) * kDepth * 4) * 32 + lane;   // [depth][piece][lane]
+    const int n_chunks = K > warp * kChunk ? (K - warp * kChunk + kWarps * kChunk - 1) / (kWarps * kChunk) : 0;
+    auto issue_chunk = [&](int index) {
+        if (index < n_chunks) {
+            const int chunk = (warp + index * kWarps) * kChunk;
+            const int k_first = chunk + t * 8, k_second = chunk + 32 + t * 8;
+            uint4* slot = ring + (index % kDepth) * 4 * 32;
+            // K % 8 == 0: a group of 8 elements is whole or absent; an absent group is filled with zeros.
+            copy_async_16(slot, w_lo + (k_first < K ? k_first : 0), k_first < K);
+            copy_async_16(slot + 32, w_hi + (k_first < K ? k_first : 0), k_first < K);
+            copy_async_16(slot + 64, w_lo + (k_second < K ? k_second : 0), k_second < K);
+            copy_async_16(slot + 96, w_hi + (k_second < K ? k_second : 0), k_second < K);
+        }
+        copy_async_commit();
+    };
+#pragma unroll
+    for (int index = 0; index < kDepth - 1; ++index) issue_chunk(index);
+    grid_dependency_wait();   // the weights do not depend on the previous kernel; the activations do
+    for (int index = 0; index < n_chunks; ++index) {
+        issue_chunk(index + kDepth - 1);
+        const int chunk = (warp + index * kWarps) * kChunk;
         const int k_first = chunk + t * 8, k_second = chunk + 32 + t * 8;
-        const bool first_live = k_first < K, second_live = k_second < K;   // K % 8 == 0: a group of 8 is whole or absent
-        const uint4 lo1 = first_live ? __ldcs(reinterpret_cast<const uint4*>(w_lo + k_first)) : zero;
-        const uint4 hi1 = first_live ? __ldcs(reinterpret_cast<const uint4*>(w_hi + k_first)) : zero;
-        const uint4 lo2 = second_live ? __ldcs(reinterpret_cast<const uint4*>(w_lo + k_second)) : zero;
-        const uint4 hi2 = second_live ? __ldcs(reinterpret_cast<const uint4*>(w_hi + k_second)) : zero;
+        const bool first_live = k_first < K, second_live = k_second < K;
+        uint4 x1[NB], x2[NB];
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            const uint4 x1 = (x_live[j] && first_live) ? __ldg(reinterpret_cast<const uint4*>(x_row[j] + k_first)) : zero;
-            const uint4 x2 = (x_live[j] && second_live) ? __ldg(reinterpret_cast<const uint4*>(x_row[j] + k_second)) : zero;
-            mma_bf16(acc[j], lo1.x, hi1.x, lo1.y, hi1.y, x1.x, x1.y);
-            mma_bf16(acc[j], lo1.z, hi1.z, lo1.w, hi1.w, x1.z, x1.w);
-            mma_bf16(acc[j], lo2.x, hi2.x, lo2.y, hi2.y, x2.x, x2.y);
-            mma_bf16(acc[j], lo2.z, hi2.z, lo2.w, hi2.w, x2.z, x2.w);
+            x1[j] = (x_live[j] && first_live) ? __ldg(reinterpret_cast<const uint4*>(x_row[j] + k_first)) : zero;
+            x2[j] = (x_live[j] && second_live) ? __ldg(reinterpret_cast<const uint4*>(x_row[j] + k_second)) : zero;
+        }
+        copy_async_wait<kDepth - 1>();   // this lane's pieces of chunk `index` have landed
+        const uint4* slot = ring + (index % kDepth) * 4 * 32;
+        const uint4 lo1 = slot[0], hi1 = slot[32], lo2 = slot[64], hi2 = slot[96];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            mma_bf16(acc[j], lo1.x, hi1.x, lo1.y, hi1.y, x1[j].x, x1[j].y);
+            mma_bf16(acc[j], lo1.z, hi1.z, lo1.w, hi1.w, x1[j].z, x1[j].w);
+            mma_bf16(acc[j], lo2.x, hi2.x, lo2.y, hi2.y, x2[j].x, x2[j].y);
+            mma_bf16(acc[j], lo2.z, hi2.z, lo2.w, hi2.w, x2[j].z, x2[j].w);
         }
     }
+    copy_async_wait<0>();
+    __syncthreads();   // the ring is done with; its memory now holds the warps' partial sums
+    float (*partial)[NB * 8][kRows + 1] = reinterpret_cast<float (*)[NB * 8][kRows + 1]>(ring_raw);
     // acc[j] = {D[g][2t], D[g][2t+1], D[g+8][2t], D[g+8][2t+1]} with D[feature][token within block j].
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
@@ -101,11 +154,18 @@ template <int NB>
 int launch(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride,
            long long w_stride, long long out_stride, cudaStream_t stream) {
     const unsigned blocks = (N + kRows - 1) / kRows;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        if (status == cudaSuccess) status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        configured = true;
+    }
     if (out_dtype == TAU_BF16)
-        tau_launch(gemm_skinny_kernel<NB, bf16>, dim3(blocks), dim3(kWarps * 32), 0, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, bf16>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                         static_cast<bf16*>(out), M, N, K, x_stride, w_stride, out_stride);
     else
-        tau_launch(gemm_skinny_kernel<NB, float>, dim3(blocks), dim3(kWarps * 32), 0, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, float>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                          static_cast<float*>(out), M, N, K, x_stride, w_stride, out_stride);
     return tau_launch_status();
 }
