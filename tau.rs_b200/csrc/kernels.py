@@ -284,12 +284,14 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
 def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     """Number of context splits that decode attention uses for this many sequences of at most this length.
 
-    `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  The aim is about
-    four blocks per SM in all, each split at least 64 positions long.  The length is rounded up to a power of two
-    first, so that a captured graph (whose key holds this number) serves a whole range of lengths.
+    `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Two blocks of the
+    decode kernel fit an SM, so the aim is the largest number of splits whose blocks are all resident at once
+    (one wave: a second, partly filled wave costs more than the extra parallelism gives), each split at least 64
+    positions long.  The length is rounded up to a power of two first, so that a captured graph (whose key holds
+    this number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
-    wanted = -(-592 // max(1, n_seqs * kv_blocks))
+    wanted = max(1, 296 // max(1, n_seqs * kv_blocks))
     return max(1, min(wanted, bucket // 64, 64))
 
 
