@@ -250,16 +250,59 @@ __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
     return *reinterpret_cast<const unsigned*>(&pair);
 }
 
+// What the fused form needs to prepare queries and the new key and value itself (decode_attention.cu:120-181 of the
+// reference does this in a kernel of its own).  `projected == nullptr`: queries are ready and the cache is complete.
+struct DecodePrepare {
+    const bf16* projected;        // [sequences, (n_heads + 2 n_kv_heads) D] as the stacked projection left it
+    long long projected_stride;
+    const float* q_weight;        // per-head norm weights, or nullptr for no norm
+    const float* k_weight;
+    float eps;
+    const float* cos_table;       // [positions, rotary_dim / 2], or nullptr
+    const float* sin_table;
+    int rotary_dim;
+    int write_cache;              // 0: another run wrote this position's key and value already
+};
+
+// One warp: per-head norm (rounded to bfloat16), rotation of the first `rotary_dim` elements in 32-bit, rounded again.
+__device__ __forceinline__ void prepare_head(const bf16* __restrict__ source, const float* __restrict__ weight, float eps,
+                                             const float* __restrict__ cos_row, const float* __restrict__ sin_row, int rotary_dim,
+                                             bf16* __restrict__ target, int lane) {
+    float inverse = 1.0f;
+    if (weight) {
+        float squares = 0.0f;
+        for (int e = lane; e < D; e += 32) {
+            const float value = __bfloat162float(source[e]);
+            squares += value * value;
+        }
+        inverse = rsqrtf(warp_sum(squares) / static_cast<float>(D) + eps);
+    }
+    auto normalized = [&](int e) {
+        const float value = __bfloat162float(source[e]);
+        return weight ? __bfloat162float(__float2bfloat16_rn(value * inverse * weight[e])) : value;
+    };
+    const int half = rotary_dim / 2;
+    for (int j = lane; j < half; j += 32) {
+        const float first = normalized(j), second = normalized(j + half);
+        const float c = cos_row[j], s = sin_row[j];
+        target[j] = __float2bfloat16_rn(first * c - second * s);
+        target[j + half] = __float2bfloat16_rn(second * c + first * s);
+    }
+    for (int e = rotary_dim + lane; e < D; e += 32) target[e] = __float2bfloat16_rn(normalized(e));
+}
+
 template <int GH>
 __global__ void __launch_bounds__(kWarps * 32)
-decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restrict__ keys, const bf16* __restrict__ values,
-                          bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ keys, bf16* __restrict__ values,
+                          bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml, int* __restrict__ tickets,
                           const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
-                          int n_heads, int n_kv_heads, int passes, float scale, int window, int splits) {
+                          int n_heads, int n_kv_heads, int passes, float scale, int window, int splits, DecodePrepare prepare) {
     grid_dependents_launch();
     grid_dependency_wait();
     __shared__ float merge_o[kWarps][GH][D];
     __shared__ float merge_ml[kWarps][GH][2];
+    __shared__ __align__(16) bf16 q_shared[GH][D];
+    __shared__ int is_last_block;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, seq = blockIdx.z;
@@ -274,28 +317,47 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
     const int lo = first + split * per_split;
     const int hi = min(length, lo + per_split);
     const size_t record = (static_cast<size_t>(seq) * n_heads + head0) * splits + split;
-
-    if (lo >= hi) {
-        if (splits > 1 && threadIdx.x < heads_here) {
-            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2] = -INFINITY;
-            partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2 + 1] = 0.0f;
-        }
-        return;
-    }
+    const int* pages = page_rows + static_cast<size_t>(seq) * page_stride;
+    const size_t head_stride = static_cast<size_t>(page_tokens) * D;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+    if (prepare.projected != nullptr && lo < hi) {
+        // Tasks: the query heads of this pass; and, in the block whose range holds the newest position, its key and value.
+        const int position = length - 1;
+        const bool owns_newest = prepare.write_cache && pass == 0 && lo <= position && position < hi;
+        const bf16* row = prepare.projected + static_cast<size_t>(seq) * prepare.projected_stride;
+        const float* cos_row = prepare.rotary_dim ? prepare.cos_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
+        const float* sin_row = prepare.rotary_dim ? prepare.sin_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
+        const size_t newest = (static_cast<size_t>(pages[position / page_tokens]) * n_kv_heads + kv_head) * head_stride +
+                              static_cast<size_t>(position % page_tokens) * D;
+        for (int task = warp; task < heads_here + (owns_newest ? 2 : 0); task += kWarps) {
+            if (task < heads_here) {
+                prepare_head(row + static_cast<size_t>(head0 + task) * D, prepare.q_weight, prepare.eps, cos_row, sin_row, prepare.rotary_dim,
+                             q_shared[task], lane);
+            } else if (task == heads_here) {
+                prepare_head(row + static_cast<size_t>(n_heads + kv_head) * D, prepare.k_weight, prepare.eps, cos_row, sin_row,
+                             prepare.rotary_dim, keys + newest, lane);
+            } else {
+                const bf16* source = row + static_cast<size_t>(n_heads + n_kv_heads + kv_head) * D;
+                for (int e = lane; e < D; e += 32) values[newest + e] = source[e];
+            }
+        }
+        __threadfence();   // the newest key and value are read back from the cache by this block below
+    }
+    __syncthreads();
+
     // Query fragments: head g of this pass, elements 32 c + 8 t .. + 8 of chunk c.
     uint4 q_frag[kQkChunks];
     {
-        const bool head_live = g < heads_here;
-        const bf16* q_row = queries + (static_cast<size_t>(seq) * n_heads + head0 + (head_live ? g : 0)) * D;
+        const bool head_live = g < heads_here && lo < hi;
+        const bf16* q_row = prepare.projected != nullptr ? q_shared[head_live ? g : 0]
+                                                         : queries + (static_cast<size_t>(seq) * n_heads + head0 + (head_live ? g : 0)) * D;
 #pragma unroll
         for (int c = 0; c < kQkChunks; ++c) {
             const int e = 32 * c + 8 * t;
             q_frag[c] = (head_live && e + 8 <= D) ? *reinterpret_cast<const uint4*>(q_row + e) : zero4;
         }
     }
-    const int* pages = page_rows + static_cast<size_t>(seq) * page_stride;
-    const size_t head_stride = static_cast<size_t>(page_tokens) * D;
     const float scale_log2 = scale * 1.4426950408889634f;
     float running_max = -INFINITY, running_sum = 0.0f;   // of row g, in units of log2; the sum is this thread's share
     float acc[kRounds][8][4];
@@ -318,7 +380,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
 #pragma unroll
             for (int c = 0; c < kQkChunks; ++c) {
                 const int e = 32 * c + 8 * t;
-                k_frag[nt][c] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(key_row + e) : zero4;
+                k_frag[nt][c] = (e + 8 <= D) ? __ldcg(reinterpret_cast<const uint4*>(key_row + e)) : zero4;
             }
         }
     };
@@ -336,7 +398,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
 #pragma unroll
                 for (int r = 0; r < kRounds; ++r) {
                     const int e = 64 * r + 8 * g;
-                    v_frag[r][s] = (e + 8 <= D) ? *reinterpret_cast<const uint4*>(value_row + e) : zero4;
+                    v_frag[r][s] = (e + 8 <= D) ? __ldcg(reinterpret_cast<const uint4*>(value_row + e)) : zero4;
                 }
             }
         }
@@ -415,31 +477,62 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, const bf16* __restri
         }
     }
     __syncthreads();
+    if (lo < hi) {
+        for (int index = threadIdx.x; index < heads_here * D; index += kWarps * 32) {
+            const int h = index / D, c = index % D;
+            float total_max = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) total_max = fmaxf(total_max, merge_ml[w][h][0]);
+            float o = 0.0f, sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float factor = exp2f(merge_ml[w][h][0] - total_max);   // 0 for a warp that saw no key
+                if (factor > 0.0f) {
+                    o += merge_o[w][h][c] * factor;
+                    sum += merge_ml[w][h][1] * factor;
+                }
+            }
+            if (splits == 1) {
+                out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
+            } else {
+                const size_t slot = record + static_cast<size_t>(h) * splits;
+                partial_o[slot * D + c] = o;
+                if (c == 0) {
+                    partial_ml[slot * 2] = total_max * 0.6931471805599453f;   // records are kept in natural-log units
+                    partial_ml[slot * 2 + 1] = sum;
+                }
+            }
+        }
+    } else if (splits > 1 && threadIdx.x < heads_here) {   // nothing for this split: an empty record
+        partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2] = -INFINITY;
+        partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2 + 1] = 0.0f;
+    }
+    if (splits == 1) return;
+    // The block that finishes last for this sequence and KV head merges the splits' records
+    // (the reference's `combine_attention`, decode_attention.cu:255-278, without a launch of its own).
+    __threadfence();
+    __syncthreads();
+    int* ticket = tickets + static_cast<size_t>(seq) * gridDim.y + blockIdx.y;
+    if (threadIdx.x == 0) is_last_block = atomicAdd(ticket, 1) == splits - 1;
+    __syncthreads();
+    if (!is_last_block) return;
+    __threadfence();
     for (int index = threadIdx.x; index < heads_here * D; index += kWarps * 32) {
         const int h = index / D, c = index % D;
+        const size_t base = (static_cast<size_t>(seq) * n_heads + head0 + h) * splits;
         float total_max = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) total_max = fmaxf(total_max, merge_ml[w][h][0]);
+        for (int s = 0; s < splits; ++s) total_max = fmaxf(total_max, __ldcg(partial_ml + (base + s) * 2));
         float o = 0.0f, sum = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float factor = exp2f(merge_ml[w][h][0] - total_max);   // 0 for a warp that saw no key
-            if (factor > 0.0f) {
-                o += merge_o[w][h][c] * factor;
-                sum += merge_ml[w][h][1] * factor;
+        for (int s = 0; s < splits; ++s) {
+            const float factor = __expf(__ldcg(partial_ml + (base + s) * 2) - total_max);
+            if (factor > 0.0f) {   // an empty split wrote no context
+                o += __ldcg(partial_o + (base + s) * D + c) * factor;
+                sum += __ldcg(partial_ml + (base + s) * 2 + 1) * factor;
             }
         }
-        if (splits == 1) {
-            out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
-        } else {
-            const size_t slot = record + static_cast<size_t>(h) * splits;
-            partial_o[slot * D + c] = o;
-            if (c == 0) {
-                partial_ml[slot * 2] = total_max * 0.6931471805599453f;   // records are kept in natural-log units
-                partial_ml[slot * 2 + 1] = sum;
-            }
-        }
+        out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
     }
+    if (threadIdx.x == 0) *ticket = 0;   // ready for the next launch
 }
 #endif  // TAU_DTYPE == 1
 
@@ -473,13 +566,27 @@ TAU_EXPORT long long tau_attention_decode_scratch(int n_seqs, int n_heads, int s
     return splits <= 1 ? 0 : static_cast<long long>(n_seqs) * n_heads * splits * (D + 2);
 }
 
-TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const void* values, void* out, const int* seq_len,
+// Ints of zeroed ticket memory that a bfloat16 launch with more than one split needs (they are left at zero).
+TAU_EXPORT long long tau_attention_decode_tickets(int n_seqs, int n_heads, int n_kv_heads) {
+    const int group = n_heads / n_kv_heads;
+    const int gh = group >= 8 ? 8 : group > 2 ? 4 : group;
+    return static_cast<long long>(n_seqs) * n_kv_heads * ((group + gh - 1) / gh);
+}
+
+// `projected` != nullptr (bfloat16 only): queries, the newest key and the newest value are taken from the stacked
+// projection `[sequences, (n_heads + 2 n_kv_heads) D]`, normalised and rotated here, and the key and value are
+// written to their cache pages (`write_cache`); `queries` is then not read.
+TAU_EXPORT int tau_attention_decode(const void* queries, void* keys, void* values, void* out, const int* seq_len,
                                     const int* page_rows, int page_stride, int page_tokens, int n_seqs, int n_heads, int n_kv_heads,
-                                    float scale, int window, int splits, float* scratch, long long scratch_floats, void* stream) {
+                                    float scale, int window, int splits, float* scratch, long long scratch_floats, int* tickets,
+                                    const void* projected, long long projected_stride, const float* q_weight, const float* k_weight,
+                                    float eps, const float* cos_table, const float* sin_table, int rotary_dim, int write_cache,
+                                    void* stream) {
     if (n_seqs <= 0) return 0;
-    if (!queries || !keys || !values || !out || !seq_len || !page_rows || n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 ||
-        page_tokens <= 0 || window < 0 || splits < 1 || splits > 256 ||
-        (splits > 1 && (!scratch || scratch_floats < tau_attention_decode_scratch(n_seqs, n_heads, splits))))
+    if ((!queries && !projected) || !keys || !values || !out || !seq_len || !page_rows || n_heads <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads != 0 || page_tokens <= 0 || window < 0 || splits < 1 || splits > 256 ||
+        (splits > 1 && (!scratch || scratch_floats < tau_attention_decode_scratch(n_seqs, n_heads, splits))) ||
+        (projected && (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || (rotary_dim > 0 && (!cos_table || !sin_table)))))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int group = n_heads / n_kv_heads;
@@ -489,23 +596,33 @@ TAU_EXPORT int tau_attention_decode(const void* queries, const void* keys, const
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + static_cast<size_t>(n_seqs) * n_heads * splits * D : nullptr;
 #if TAU_DTYPE == 1
-#define TAU_KERNEL decode_partial_mma_kernel
-#else
-#define TAU_KERNEL decode_partial_kernel
-#endif
-#define TAU_LAUNCH(GH)                                                                                                          \
-    tau_launch(TAU_KERNEL<GH>, dim3(grid), dim3(kWarps * 32), 0, s, static_cast<const T*>(queries), static_cast<const T*>(keys),          \
-                                                          static_cast<const T*>(values), static_cast<T*>(out), partial_o, partial_ml, \
-                                                          seq_len, page_rows, page_stride, page_tokens, n_heads, n_kv_heads, passes,   \
-                                                          scale, window, splits)
+    if (splits > 1 && !tickets) return cudaErrorInvalidValue;
+    DecodePrepare prepare = {static_cast<const bf16*>(projected), projected_stride, q_weight, k_weight, eps, cos_table, sin_table,
+                             rotary_dim, write_cache};
+#define TAU_LAUNCH(GH)                                                                                                             \
+    tau_launch(decode_partial_mma_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(queries), static_cast<bf16*>(keys), \
+               static_cast<bf16*>(values), static_cast<bf16*>(out), partial_o, partial_ml, tickets, seq_len, page_rows, page_stride,  \
+               page_tokens, n_heads, n_kv_heads, passes, scale, window, splits, prepare)
     if (gh == 1) TAU_LAUNCH(1);
     else if (gh == 2) TAU_LAUNCH(2);
     else if (gh == 4) TAU_LAUNCH(4);
     else TAU_LAUNCH(8);
 #undef TAU_LAUNCH
-#undef TAU_KERNEL
+    return tau_launch_status();
+#else
+    if (projected) return cudaErrorInvalidValue;   // the 32-bit path prepares with the kernel of its own
+#define TAU_LAUNCH(GH)                                                                                                             \
+    tau_launch(decode_partial_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const T*>(queries), static_cast<const T*>(keys),   \
+               static_cast<const T*>(values), static_cast<T*>(out), partial_o, partial_ml, seq_len, page_rows, page_stride,         \
+               page_tokens, n_heads, n_kv_heads, passes, scale, window, splits)
+    if (gh == 1) TAU_LAUNCH(1);
+    else if (gh == 2) TAU_LAUNCH(2);
+    else if (gh == 4) TAU_LAUNCH(4);
+    else TAU_LAUNCH(8);
+#undef TAU_LAUNCH
     int status = tau_launch_status();
     if (status || splits == 1) return status;
     tau_launch(decode_combine_kernel, dim3(n_heads, n_seqs), dim3(D < 128 ? D : 128), 0, s, partial_o, partial_ml, static_cast<T*>(out), n_heads, splits);
     return tau_launch_status();
+#endif
 }

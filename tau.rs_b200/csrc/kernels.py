@@ -296,15 +296,23 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
 
 
 _decode_scratch = {}
+_decode_tickets = {}
 
 
 def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                     window: int, splits: int) -> None:
-    """One query token per sequence (its last position) over `seq_len` cached positions, split along the context."""
+                     window: int, splits: int, prepare=None) -> None:
+    """One query token per sequence (its last position) over `seq_len` cached positions, split along the context.
+
+    `prepare` (bfloat16 only) is `(projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache)`: the kernel
+    then takes queries, the newest key and the newest value from the stacked projection itself (per-head norm,
+    rotation, cache write), `queries` may be None, and no prepare kernel is needed before it.
+    """
     _on_device(queries, keys, values, out, seq_len, page_rows)
-    n_seqs = queries.shape[0]
-    _require(queries.shape == (n_seqs, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.is_contiguous()
-             and out.dtype == queries.dtype == keys.dtype == values.dtype, "queries and output must be [sequences, n_heads * head_dim]")
+    n_seqs = out.shape[0]
+    _require(out.shape == (n_seqs, n_heads * head_dim) and out.is_contiguous() and out.dtype == keys.dtype == values.dtype,
+             "output must be [sequences, n_heads * head_dim] in the cache's dtype")
+    if queries is not None:
+        _require(queries.shape == out.shape and queries.is_contiguous() and queries.dtype == out.dtype, "queries must match the output")
     _require(head_dim % 16 == 0 and 16 <= head_dim <= 256, "head_dim must be a multiple of 16 between 16 and 256")
     _require(n_heads % n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads")
     _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
@@ -313,20 +321,59 @@ def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: in
     _require(seq_len.numel() == n_seqs and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
              and page_rows.shape[0] == n_seqs, "one length and one row of pages per sequence")
     _require(1 <= splits <= 256, "splits must lie between 1 and 256")
-    library = build.load_library("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={_code(queries)}"))
+    projected = q_weight = k_weight = cos = sin = None
+    eps, rotary_dim, write_cache = 0.0, 0, False
+    if prepare is not None:
+        projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache = prepare
+        _on_device(projected, q_weight, k_weight, cos, sin)
+        _require(out.dtype == torch.bfloat16 and projected.dtype == torch.bfloat16, "the fused form is bfloat16 only")
+        needed = (n_heads + (2 * n_kv_heads if write_cache else 0)) * head_dim
+        _require(projected.shape[0] == n_seqs and projected.shape[1] >= needed and projected.stride(1) == 1,
+                 f"projected rows must hold {needed} elements")
+        _f32_vector(q_weight, head_dim, "the q norm weight")
+        _f32_vector(k_weight, head_dim, "the k norm weight")
+        if rotary_dim:
+            _require(cos is not None and sin is not None and cos.dtype == torch.float32 and cos.shape == sin.shape
+                     and cos.shape[1] == rotary_dim // 2 and cos.is_contiguous() and sin.is_contiguous(),
+                     "rotation tables must be float32 [positions, rotary_dim / 2]")
+    else:
+        _require(queries is not None, "queries are needed unless the kernel prepares them")
+    library = build.load_library("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={_code(out)}"))
     library.tau_attention_decode_scratch.restype = ctypes.c_longlong
+    library.tau_attention_decode_tickets.restype = ctypes.c_longlong
     floats = library.tau_attention_decode_scratch(ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(splits))
-    scratch = None
+    scratch = tickets = None
     if floats:
-        key = (queries.device, torch.cuda.current_stream().cuda_stream)
+        key = (out.device, torch.cuda.current_stream().cuda_stream)
         scratch = _decode_scratch.get(key)
         if scratch is None or scratch.numel() < floats:
-            scratch = _decode_scratch[key] = torch.empty(floats, dtype=torch.float32, device=queries.device)
+            scratch = _decode_scratch[key] = torch.empty(floats, dtype=torch.float32, device=out.device)
+        if out.dtype == torch.bfloat16:
+            wanted = library.tau_attention_decode_tickets(ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads))
+            tickets = _decode_tickets.get(key)
+            if tickets is None or tickets.numel() < wanted:   # zero once; the kernel leaves them at zero
+                tickets = _decode_tickets[key] = torch.zeros(max(wanted, 1024), dtype=torch.int32, device=out.device)
+    launches = 1 if (splits == 1 or out.dtype == torch.bfloat16) else 2
     _check(library.tau_attention_decode(
         _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(seq_len), _pointer(page_rows),
         ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(splits), _pointer(scratch),
-        ctypes.c_longlong(0 if scratch is None else scratch.numel()), _stream()), "attention_decode", 1 if splits == 1 else 2)
+        ctypes.c_longlong(0 if scratch is None else scratch.numel()), _pointer(tickets),
+        _pointer(projected), ctypes.c_longlong(0 if projected is None else projected.stride(0)), _pointer(q_weight), _pointer(k_weight),
+        ctypes.c_float(eps), _pointer(cos), _pointer(sin), ctypes.c_int(rotary_dim), ctypes.c_int(1 if write_cache else 0), _stream()),
+        "attention_decode", launches)
+
+
+def attention_decode_fused(projected, keys, values, out, step, page_rows, write_cache: bool, q_weight, k_weight, eps: float, cos, sin,
+                           rotary_dim: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int) -> bool:
+    """Prepare and decode attention in one kernel, where that exists: every sequence brings one token and the dtype is
+    bfloat16.  Returns False (and does nothing) otherwise; the caller then runs `attention_prepare` and `attention`."""
+    if not (step.all_single and projected.dtype == torch.bfloat16):
+        return False
+    splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
+    attention_decode(None, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits,
+                     prepare=(projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache))
+    return True
 
 
 def attention_prefill(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,

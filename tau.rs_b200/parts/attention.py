@@ -78,21 +78,23 @@ class Attention(Mixer):
         spec = self.spec
         # A run that only reads another run's keys and values needs its queries alone.
         projected = self.qkv.forward(hidden, rows=None if writes_cache else self.q_width)
-        queries = torch.empty((hidden.shape[0], self.q_width), dtype=hidden.dtype, device=hidden.device)
-        kernels.attention_prepare(
-            projected, queries, cache.keys, cache.values, writes_cache,
+        context = torch.empty((hidden.shape[0], self.q_width), dtype=hidden.dtype, device=hidden.device)
+        pages = step.page_rows[cache.group]
+        prepare = (
             None if self.q_norm is None else self.q_norm.weight,
             None if self.k_norm is None else self.k_norm.weight,
             0.0 if spec.qk_norm is None else spec.qk_norm.eps,
             None if self.position is None else self.position.cos,
             None if self.position is None else self.position.sin,
             0 if self.position is None else spec.position.rotary_dim,
-            step.positions, step.token_seq, step.page_rows[cache.group],
-            spec.n_heads, spec.n_kv_heads, spec.head_dim,
         )
-        context = torch.empty_like(queries)
-        kernels.attention(
-            queries, cache.keys, cache.values, context, step, step.page_rows[cache.group],
-            spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.softmax_scale, spec.window or 0,
-        )
+        # One token per sequence in bfloat16: norm, rotation, cache write and attention are one kernel.
+        if kernels.attention_decode_fused(projected, cache.keys, cache.values, context, step, pages, writes_cache, *prepare,
+                                          spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.softmax_scale, spec.window or 0):
+            return self.out.forward(context)
+        queries = torch.empty_like(context)
+        kernels.attention_prepare(projected, queries, cache.keys, cache.values, writes_cache, *prepare,
+                                  step.positions, step.token_seq, pages, spec.n_heads, spec.n_kv_heads, spec.head_dim)
+        kernels.attention(queries, cache.keys, cache.values, context, step, pages, spec.n_heads, spec.n_kv_heads, spec.head_dim,
+                          spec.softmax_scale, spec.window or 0)
         return self.out.forward(context)

@@ -111,6 +111,10 @@ def decode_splits(n_seqs, max_len, kv_blocks=8):
     return 1
 
 
+def attention_decode_fused(*args, **kwargs):
+    return False     # the plain statement keeps prepare and attention apart
+
+
 def attention(queries, keys, values, out, step, page_rows, n_heads, n_kv_heads, head_dim, scale, window):
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
 
@@ -171,7 +175,7 @@ def sample_gumbel(logits, tokens, valid, inverse_temperature, seed, request_ids,
 
 
 ALL = ("embedding", "rms_norm", "add_rms_norm", "silu_mul", "linear", "gemm_simt", "attention_prepare", "attention_generic",
-       "attention", "decode_splits", "argmax", "sample_gumbel")
+       "attention", "attention_decode_fused", "decode_splits", "argmax", "sample_gumbel")
 
 
 def install(monkeypatch):

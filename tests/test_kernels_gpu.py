@@ -299,6 +299,43 @@ def test_decode_attention_splits_and_groups(dtype, n_heads, n_kv_heads, head_dim
         close(found, wanted, dtype)
 
 
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,rotary_dim,with_norm,window", [
+    (8, 2, 128, 128, True, 0), (4, 4, 16, 16, True, 0), (6, 3, 48, 16, False, 0), (16, 1, 64, 64, True, 0), (4, 1, 32, 32, True, 20)])
+def test_fused_decode_attention(n_heads, n_kv_heads, head_dim, rotary_dim, with_norm, window):
+    """Norm, rotation, cache write and split attention in one kernel against the plain prepare followed by plain attention."""
+    dtype = torch.bfloat16
+    lengths = [1, 64, 65, 300, 130]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, [1] * 5, n_kv_heads, head_dim, dtype, seed=80, pages=24)
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    projected = randn(5, width, dtype=dtype, seed=81)
+    generator = torch.Generator().manual_seed(82)
+    q_weight = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(DEVICE) if with_norm else None
+    k_weight = (1 + 0.1 * torch.randn(head_dim, generator=generator)).to(DEVICE) if with_norm else None
+    angles = torch.rand(400, rotary_dim // 2, generator=generator) * 6.0
+    cos, sin = torch.cos(angles).to(DEVICE), torch.sin(angles).to(DEVICE)
+    seq_len = torch.tensor(lengths, dtype=torch.int32, device=DEVICE)
+    cpu = lambda t: None if t is None else t.cpu()
+    for write in (True, False):
+        wanted_k, wanted_v = keys.cpu().clone(), values.cpu().clone()
+        wanted_q = torch.empty(5, n_heads * head_dim, dtype=dtype)
+        plain_kernels.attention_prepare(projected.cpu(), wanted_q, wanted_k, wanted_v, write, cpu(q_weight), cpu(k_weight), 1e-6, cpu(cos),
+                                        cpu(sin), rotary_dim, positions.cpu(), token_seq.cpu(), rows.cpu(), n_heads, n_kv_heads, head_dim)
+        wanted = torch.empty(5, n_heads * head_dim, dtype=dtype)
+        plain_kernels.attention_generic(wanted_q, wanted_k, wanted_v, wanted, positions.cpu(), token_seq.cpu(), rows.cpu(), n_heads,
+                                        n_kv_heads, head_dim, head_dim ** -0.5, window)
+        for splits in (1, 3, 8):
+            found_k, found_v = keys.clone(), values.clone()
+            found = torch.full((5, n_heads * head_dim), float("nan"), dtype=dtype, device=DEVICE)
+            kernels.attention_decode(None, found_k, found_v, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window,
+                                     splits, prepare=(projected, q_weight, k_weight, 1e-6, cos, sin, rotary_dim, write))
+            close(found, wanted, dtype)
+            close(found_k, wanted_k, dtype)
+            assert torch.equal(found_v.cpu(), wanted_v)
+            kernels.attention_decode(None, found_k, found_v, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window,
+                                     splits, prepare=(projected, q_weight, k_weight, 1e-6, cos, sin, rotary_dim, write))
+            close(found, wanted, dtype)     # a second launch finds the tickets at zero again
+
+
 def adversarial_rows():
     nan, inf = float("nan"), float("inf")
     rows = [
