@@ -229,13 +229,15 @@ decode_partial_kernel(const T* __restrict__ queries, const T* __restrict__ keys,
 
 #if TAU_DTYPE == 1
 // ---- bfloat16: the same split on the tensor cores ----------------------------------------------------------
-// A warp takes blocks of 16 keys.  Scores are mma.sync m16n8k16 products with the group's query heads as the
-// rows of A (rows beyond the group are zero) and the keys as the columns of B; a thread's 16-byte load of a key
-// row (8 consecutive elements) feeds two products, which permutes the head dimension inside a chunk of 32
-// identically for queries and keys.  Probabilities stay in registers: the C fragments of two key tiles are
-// the A fragment of the second product, whose B fragments are built from 16-byte loads of value rows (one key,
-// 8 consecutive columns per load) with byte permutes; output column `64 r + 8 n + j` sits in column slot `n` of
-// tile `j` of round `r`, so a thread ends up owning 16 consecutive columns of each round.
+// A warp takes blocks of 16 keys and works on the transposed problem, so that the 16 rows of a product are keys (all
+// of them real) and its 8 columns are the group's query heads: scores S^T = K Q^T are mma.sync m16n8k16 products
+// whose A fragments are 16-byte loads of two key rows (8 consecutive elements each; a load feeds two products,
+// which permutes the head dimension inside a chunk of 32 identically for keys and queries).  A thread then holds
+// the scores of keys g and g + 8 for heads 2t and 2t + 1, keeps the running maximum and sum of its two heads
+// itself, and turns its probabilities into the B fragment of the second product, O^T = V^T P, with two movmatrix
+// transposes.  The A fragments of that product are assembled from 16-byte loads of value rows (one key, 8
+// consecutive columns) with byte permutes: row g of tile i in round r is output column 64 r + 8 g + 2 i, row g + 8
+// the column after it.  Accumulators are 4 registers per 16 output columns, half of what the untransposed form needs.
 constexpr int kQkChunks = (D + 31) / 32;   // chunks of 32 head elements for the score products
 constexpr int kRounds = (D + 63) / 64;     // rounds of 64 output columns
 
@@ -291,8 +293,11 @@ __device__ __forceinline__ void prepare_head(const bf16* __restrict__ source, co
     for (int e = rotary_dim + lane; e < D; e += 32) target[e] = __float2bfloat16_rn(normalized(e));
 }
 
+#ifndef TAU_DECODE_MIN_BLOCKS
+#define TAU_DECODE_MIN_BLOCKS 4
+#endif
 template <int GH>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, TAU_DECODE_MIN_BLOCKS)
 decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ keys, bf16* __restrict__ values,
                           bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml, int* __restrict__ tickets,
                           const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
@@ -324,7 +329,8 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
     if (prepare.projected != nullptr && lo < hi) {
         // Tasks: the query heads of this pass; and, in the block whose range holds the newest position, its key and value.
         const int position = length - 1;
-        const bool owns_newest = prepare.write_cache && pass == 0 && lo <= position && position < hi;
+        // Every pass needs the newest row, so every pass whose range holds it writes it (the same values) and reads its own.
+        const bool owns_newest = prepare.write_cache && lo <= position && position < hi;
         const bf16* row = prepare.projected + static_cast<size_t>(seq) * prepare.projected_stride;
         const float* cos_row = prepare.rotary_dim ? prepare.cos_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
         const float* sin_row = prepare.rotary_dim ? prepare.sin_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
@@ -346,7 +352,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
     }
     __syncthreads();
 
-    // Query fragments: head g of this pass, elements 32 c + 8 t .. + 8 of chunk c.
+    // Query fragments (B operand of the score product): head g of this pass, elements 32 c + 8 t .. + 8 of chunk c.
     uint4 q_frag[kQkChunks];
     {
         const bool head_live = g < heads_here && lo < hi;
@@ -359,36 +365,23 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
         }
     }
     const float scale_log2 = scale * 1.4426950408889634f;
-    float running_max = -INFINITY, running_sum = 0.0f;   // of row g, in units of log2; the sum is this thread's share
-    float acc[kRounds][8][4];
+    // This thread's two heads, 2t and 2t + 1: running maximum (log2 units) and this thread's share of the sum.
+    float running_max[2] = {-INFINITY, -INFINITY}, running_sum[2] = {0.0f, 0.0f};
+    float acc[kRounds][4][4];   // [round][tile][c0..c3]: c0, c1 = column 64 r + 8 g + 2 i of heads 2t, 2t+1; c2, c3 = the column after it
 #pragma unroll
     for (int r = 0; r < kRounds; ++r)
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[r][j][i] = 0.0f;
+            for (int j = 0; j < 4; ++j) acc[r][i][j] = 0.0f;
 
     auto row_offset = [&](int key) {   // a key beyond the range is replaced by the last one; its probability is zero
         const int k = min(key, hi - 1);
         return (static_cast<size_t>(pages[k / page_tokens]) * n_kv_heads + kv_head) * head_stride + static_cast<size_t>(k % page_tokens) * D;
     };
 
-    auto load_keys = [&](int base, uint4 (&k_frag)[2][kQkChunks]) {   // key rows base + 8 nt + g
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const bf16* key_row = keys + row_offset(base + 8 * nt + g);
-#pragma unroll
-            for (int c = 0; c < kQkChunks; ++c) {
-                const int e = 32 * c + 8 * t;
-                k_frag[nt][c] = (e + 8 <= D) ? __ldcg(reinterpret_cast<const uint4*>(key_row + e)) : zero4;
-            }
-        }
-    };
-    // Software pipeline: the values of a block are requested before its scores are computed, and the keys of
-    // the next block right after, so each load has a product and a softmax to arrive behind.
-    uint4 k_frag[2][kQkChunks];
-    if (lo + warp * 16 < hi) load_keys(lo + warp * 16, k_frag);
     for (int base = lo + warp * 16; base < hi; base += kWarps * 16) {
+        // Value rows of keys base + {2t, 2t+1, 2t+8, 2t+9}, columns 64 r + 8 g .. + 8: requested together with the keys, used after the softmax.
         uint4 v_frag[kRounds][4];
         {
             const int slots[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
@@ -402,45 +395,50 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
                 }
             }
         }
-        // Scores of 16 keys: two tiles of 8.
-        float score[2][4];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) score[nt][i] = 0.0f;
+        // Scores of 16 keys x 8 heads: rows g and g + 8 are keys base + g and base + g + 8.
+        float score[4] = {0.0f, 0.0f, 0.0f, 0.0f}, score_odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const bf16* key_lo = keys + row_offset(base + g);
+            const bf16* key_hi = keys + row_offset(base + g + 8);
+            uint4 k_lo[kQkChunks], k_hi[kQkChunks];
 #pragma unroll
             for (int c = 0; c < kQkChunks; ++c) {
-                mma_bf16(score[nt], q_frag[c].x, 0u, q_frag[c].y, 0u, k_frag[nt][c].x, k_frag[nt][c].y);
-                mma_bf16(score[nt], q_frag[c].z, 0u, q_frag[c].w, 0u, k_frag[nt][c].z, k_frag[nt][c].w);
+                const int e = 32 * c + 8 * t;
+                k_lo[c] = (e + 8 <= D) ? __ldcg(reinterpret_cast<const uint4*>(key_lo + e)) : zero4;
+                k_hi[c] = (e + 8 <= D) ? __ldcg(reinterpret_cast<const uint4*>(key_hi + e)) : zero4;
+            }
+#pragma unroll
+            for (int c = 0; c < kQkChunks; ++c) {   // two chains, so that consecutive products do not wait for each other
+                mma_bf16(score, k_lo[c].x, k_hi[c].x, k_lo[c].y, k_hi[c].y, q_frag[c].x, q_frag[c].y);
+                mma_bf16(score_odd, k_lo[c].z, k_hi[c].z, k_lo[c].w, k_hi[c].w, q_frag[c].z, q_frag[c].w);
             }
         }
-        if (base + kWarps * 16 < hi) load_keys(base + kWarps * 16, k_frag);
-        // Row g holds keys base + 8 nt + 2t + {0, 1} in score[nt][0..1].
-        float block_max = -INFINITY;
+        // score[0], [1]: key base + g, heads 2t and 2t + 1; score[2], [3]: key base + g + 8, the same heads.
+        const bool live_lo = base + g < hi, live_hi = base + g + 8 < hi;
+        float block_max[2];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int h = 0; h < 2; ++h) {
+            score[h] = live_lo ? (score[h] + score_odd[h]) * scale_log2 : -INFINITY;
+            score[2 + h] = live_hi ? (score[2 + h] + score_odd[2 + h]) * scale_log2 : -INFINITY;
+            block_max[h] = fmaxf(score[h], score[2 + h]);
+            block_max[h] = fmaxf(block_max[h], __shfl_xor_sync(0xffffffffu, block_max[h], 4));
+            block_max[h] = fmaxf(block_max[h], __shfl_xor_sync(0xffffffffu, block_max[h], 8));
+            block_max[h] = fmaxf(block_max[h], __shfl_xor_sync(0xffffffffu, block_max[h], 16));
+        }
+        float correction[2], p[4];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = base + 8 * nt + 2 * t + e;
-                score[nt][e] = key < hi ? score[nt][e] * scale_log2 : -INFINITY;
-                block_max = fmaxf(block_max, score[nt][e]);
-            }
-        block_max = fmaxf(block_max, __shfl_xor_sync(0xffffffffu, block_max, 1));
-        block_max = fmaxf(block_max, __shfl_xor_sync(0xffffffffu, block_max, 2));
-        const float new_max = fmaxf(running_max, block_max);     // finite: key `base` is inside the range
-        const float correction = exp2f(running_max - new_max);
-        running_max = new_max;
-        float p[2][2];
-        float block_sum_share = 0.0f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                p[nt][e] = exp2f(score[nt][e] - new_max);
-                block_sum_share += p[nt][e];
-            }
-        running_sum = running_sum * correction + block_sum_share;
-        const unsigned pa0 = pack_bf16(p[0][0], p[0][1]), pa2 = pack_bf16(p[1][0], p[1][1]);
+        for (int h = 0; h < 2; ++h) {
+            const float new_max = fmaxf(running_max[h], block_max[h]);   // finite: key `base` is inside the range
+            correction[h] = exp2f(running_max[h] - new_max);
+            running_max[h] = new_max;
+            p[h] = exp2f(score[h] - new_max);
+            p[2 + h] = exp2f(score[2 + h] - new_max);
+            running_sum[h] = running_sum[h] * correction[h] + p[h] + p[2 + h];
+        }
+        // Probabilities as the B operand of the second product: transpose (key on g, head on t) into (key on t, head on g).
+        unsigned pb0 = pack_bf16(p[0], p[1]), pb1 = pack_bf16(p[2], p[3]);
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pb0));
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pb1));
 #pragma unroll
         for (int r = 0; r < kRounds; ++r) {
             const unsigned* k0 = reinterpret_cast<const unsigned*>(&v_frag[r][0]);   // key 2t
@@ -448,32 +446,43 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
             const unsigned* k8 = reinterpret_cast<const unsigned*>(&v_frag[r][2]);   // key 2t + 8
             const unsigned* k9 = reinterpret_cast<const unsigned*>(&v_frag[r][3]);   // key 2t + 9
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                // Column j of each row is halfword j of its vector: word j / 2, low or high half.
-                const unsigned selector = (j & 1) ? 0x7632u : 0x5410u;
-                const unsigned b0 = __byte_perm(k0[j >> 1], k1[j >> 1], selector);
-                const unsigned b1 = __byte_perm(k8[j >> 1], k9[j >> 1], selector);
-                acc[r][j][0] *= correction;
-                acc[r][j][1] *= correction;
-                mma_bf16(acc[r][j], pa0, 0u, pa2, 0u, b0, b1);
+            for (int i = 0; i < 4; ++i) {
+                // Word i of a vector holds columns 2 i (low half) and 2 i + 1 (high half) of its key.
+                const unsigned a0 = __byte_perm(k0[i], k1[i], 0x5410u), a1 = __byte_perm(k0[i], k1[i], 0x7632u);
+                const unsigned a2 = __byte_perm(k8[i], k9[i], 0x5410u), a3 = __byte_perm(k8[i], k9[i], 0x7632u);
+                acc[r][i][0] *= correction[0];
+                acc[r][i][1] *= correction[1];
+                acc[r][i][2] *= correction[0];
+                acc[r][i][3] *= correction[1];
+                mma_bf16(acc[r][i], a0, a1, a2, a3, pb0, pb1);
             }
         }
     }
-    // This warp's row g: the sum over the four threads of the row; columns 64 r + 16 t + j (c0) and + 8 (c1).
-    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
-    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
-    if (g < GH) {
+    // Sums over the keys of this warp: over the 8 threads that share t.
 #pragma unroll
-        for (int r = 0; r < kRounds; ++r)
+    for (int h = 0; h < 2; ++h) {
+        running_sum[h] += __shfl_xor_sync(0xffffffffu, running_sum[h], 4);
+        running_sum[h] += __shfl_xor_sync(0xffffffffu, running_sum[h], 8);
+        running_sum[h] += __shfl_xor_sync(0xffffffffu, running_sum[h], 16);
+    }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c0 = 64 * r + 16 * t + j, c1 = c0 + 8;
-                if (c0 < D) merge_o[warp][g][c0] = acc[r][j][0];
-                if (c1 < D) merge_o[warp][g][c1] = acc[r][j][1];
+    for (int h = 0; h < 2; ++h) {
+        const int head = 2 * t + h;
+        if (head < GH) {
+#pragma unroll
+            for (int r = 0; r < kRounds; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c0 = 64 * r + 8 * g + 2 * i;
+                    if (c0 < D) {
+                        merge_o[warp][head][c0] = acc[r][i][h];
+                        merge_o[warp][head][c0 + 1] = acc[r][i][2 + h];
+                    }
+                }
+            if (g == 0) {
+                merge_ml[warp][head][0] = running_max[h];
+                merge_ml[warp][head][1] = running_sum[h];
             }
-        if (t == 0) {
-            merge_ml[warp][g][0] = running_max;
-            merge_ml[warp][g][1] = running_sum;
         }
     }
     __syncthreads();
@@ -517,20 +526,41 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
     __syncthreads();
     if (!is_last_block) return;
     __threadfence();
+    // The records' maxima and sums go through shared memory first (one round trip for all of them), so that the
+    // sums over the splits below are independent loads and not a chain.  The merge buffers are free by now.
+    float* record_max = &merge_o[0][0][0];               // [heads_here][splits]
+    float* record_sum = record_max + GH * splits;        // [heads_here][splits]   (2 GH splits <= kWarps GH D floats: splits <= 2 D)
+    for (int index = threadIdx.x; index < heads_here * splits; index += kWarps * 32) {
+        const int h = index / splits, s = index % splits;
+        const size_t slot = (static_cast<size_t>(seq) * n_heads + head0 + h) * splits + s;
+        record_max[h * splits + s] = __ldcg(partial_ml + slot * 2);
+        record_sum[h * splits + s] = __ldcg(partial_ml + slot * 2 + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < heads_here) {   // per head: the factor of each split, and one over the total sum in merge_ml[0][h][0]
+        const int h = threadIdx.x;
+        float total_max = -INFINITY;
+        for (int s = 0; s < splits; ++s) total_max = fmaxf(total_max, record_max[h * splits + s]);
+        float sum = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float factor = __expf(record_max[h * splits + s] - total_max);   // 0 for an empty split
+            sum += record_sum[h * splits + s] * factor;
+            record_max[h * splits + s] = factor;
+        }
+        merge_ml[0][h][0] = 1.0f / sum;
+    }
+    __syncthreads();
     for (int index = threadIdx.x; index < heads_here * D; index += kWarps * 32) {
         const int h = index / D, c = index % D;
-        const size_t base = (static_cast<size_t>(seq) * n_heads + head0 + h) * splits;
-        float total_max = -INFINITY;
-        for (int s = 0; s < splits; ++s) total_max = fmaxf(total_max, __ldcg(partial_ml + (base + s) * 2));
-        float o = 0.0f, sum = 0.0f;
+        const float* column = partial_o + (static_cast<size_t>(seq) * n_heads + head0 + h) * splits * D + c;
+        float o = 0.0f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float factor = __expf(__ldcg(partial_ml + (base + s) * 2) - total_max);
-            if (factor > 0.0f) {   // an empty split wrote no context
-                o += __ldcg(partial_o + (base + s) * D + c) * factor;
-                sum += __ldcg(partial_ml + (base + s) * 2 + 1) * factor;
-            }
+            const float factor = record_max[h * splits + s];
+            const float value = __ldcg(column + static_cast<size_t>(s) * D);
+            o += factor > 0.0f ? value * factor : 0.0f;   // an empty split wrote no context: whatever lies there is not used
         }
-        out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
+        out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o * merge_ml[0][h][0]);
     }
     if (threadIdx.x == 0) *ticket = 0;   // ready for the next launch
 }
@@ -596,7 +626,7 @@ TAU_EXPORT int tau_attention_decode(const void* queries, void* keys, void* value
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + static_cast<size_t>(n_seqs) * n_heads * splits * D : nullptr;
 #if TAU_DTYPE == 1
-    if (splits > 1 && !tickets) return cudaErrorInvalidValue;
+    if (splits > 1 && (!tickets || splits > 2 * D)) return cudaErrorInvalidValue;   // the merge reuses 2 GH splits floats of shared memory
     DecodePrepare prepare = {static_cast<const bf16*>(projected), projected_stride, q_weight, k_weight, eps, cos_table, sin_table,
                              rotary_dim, write_cache};
 #define TAU_LAUNCH(GH)                                                                                                             \

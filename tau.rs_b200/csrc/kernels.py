@@ -284,15 +284,15 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
 def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     """Number of context splits that decode attention uses for this many sequences of at most this length.
 
-    `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Two blocks of the
+    `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Four blocks of the
     decode kernel fit an SM, so the aim is the largest number of splits whose blocks are all resident at once
     (one wave: a second, partly filled wave costs more than the extra parallelism gives), each split at least 64
     positions long.  The length is rounded up to a power of two first, so that a captured graph (whose key holds
     this number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
-    wanted = max(1, 296 // max(1, n_seqs * kv_blocks))
-    return max(1, min(wanted, bucket // 64, 64))
+    wanted = max(1, 592 // max(1, n_seqs * kv_blocks))
+    return max(1, min(wanted, bucket // 64, 32))
 
 
 _decode_scratch = {}
@@ -320,7 +320,7 @@ def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: in
     _int_vector(seq_len, "sequence lengths")
     _require(seq_len.numel() == n_seqs and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
              and page_rows.shape[0] == n_seqs, "one length and one row of pages per sequence")
-    _require(1 <= splits <= 256, "splits must lie between 1 and 256")
+    _require(1 <= splits <= 256 and (out.dtype != torch.bfloat16 or splits <= 2 * head_dim), "splits must lie between 1 and 256 (and 2 * head_dim in bfloat16)")
     projected = q_weight = k_weight = cos = sin = None
     eps, rotary_dim, write_cache = 0.0, 0, False
     if prepare is not None:
