@@ -83,6 +83,85 @@ __global__ void attention_prepare_kernel(
     }
 }
 
+// The same for head sizes of 32 * PER elements that are rotated whole (or not at all): a lane holds PER neighbouring
+// elements, loaded and stored as one vector; the element it is paired with by the rotation lies in lane ^ 16.
+template <typename T, int PER> struct alignas(sizeof(T) * PER) HeadVector { T v[PER]; };
+
+template <typename T, int PER>
+__global__ void attention_prepare_vec_kernel(
+    const T* __restrict__ projected, long long projected_stride, T* __restrict__ queries, T* __restrict__ keys,
+    T* __restrict__ values, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int rotary_dim,
+    const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
+    int page_stride, int page_tokens, int n_heads, int n_kv_heads, int write_cache) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    constexpr int head_dim = 32 * PER;
+    typedef HeadVector<T, PER> Vector;
+    const int token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int position = positions[token];
+    const int heads_total = write_cache ? n_heads + 2 * n_kv_heads : n_heads;
+    const T* row = projected + static_cast<size_t>(token) * projected_stride;
+    size_t cache_base = 0;
+    if (write_cache) {
+        const int page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
+        cache_base = (static_cast<size_t>(page) * n_kv_heads * page_tokens + position % page_tokens) * head_dim;
+    }
+    // This lane's rotation coefficients: elements PER * (lane % 16) + i of the half-width tables.
+    float cosines[PER], sines[PER];
+    if (rotary_dim) {
+        const size_t table = static_cast<size_t>(position) * (head_dim / 2) + PER * (lane & 15);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            cosines[i] = cos_table[table + i];
+            sines[i] = sin_table[table + i];
+        }
+    }
+    for (int head = warp; head < heads_total; head += warps) {
+        const Vector loaded = *reinterpret_cast<const Vector*>(row + static_cast<size_t>(head) * head_dim + PER * lane);
+        T* target;
+        const float* weight;
+        if (head < n_heads) {
+            target = queries + (static_cast<size_t>(token) * n_heads + head) * head_dim;
+            weight = q_weight;
+        } else {
+            const int kv_head = (head - n_heads) % n_kv_heads;
+            const bool is_key = head < n_heads + n_kv_heads;
+            target = (is_key ? keys : values) + cache_base + static_cast<size_t>(kv_head) * page_tokens * head_dim;
+            weight = k_weight;
+            if (!is_key) {  // values are stored as projected
+                *reinterpret_cast<Vector*>(target + PER * lane) = loaded;
+                continue;
+            }
+        }
+        float value[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) value[i] = to_float(loaded.v[i]);
+        if (weight) {
+            float squares = 0.0f;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) squares += value[i] * value[i];
+            const float inverse = rsqrtf(warp_sum(squares) / static_cast<float>(head_dim) + eps);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) value[i] = round_through<T>(value[i] * inverse * weight[PER * lane + i]);
+        }
+        Vector result;
+        if (rotary_dim) {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const float partner = __shfl_xor_sync(0xffffffffu, value[i], 16);
+                // first half: x cos - partner sin; second half: x cos + partner sin
+                result.v[i] = from_float<T>(lane < 16 ? value[i] * cosines[i] - partner * sines[i] : value[i] * cosines[i] + partner * sines[i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < PER; ++i) result.v[i] = from_float<T>(value[i]);
+        }
+        *reinterpret_cast<Vector*>(target + PER * lane) = result;
+    }
+}
+
 // One warp per (token, query head).  Keys are taken 32 at a time: lane `l` scores key `l` of the chunk
 // with a full dot product, the chunk's maximum and sum are found by shuffles, and the values are
 // accumulated with each lane owning elements `lane, lane + 32, ...` of the head.
@@ -172,6 +251,27 @@ TAU_EXPORT int tau_attention_prepare(
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int heads_total = write_cache ? n_heads + 2 * n_kv_heads : n_heads;
     const int threads = 32 * (heads_total < 8 ? heads_total : 8);
+    // The vector form: heads of 64, 128 or 256 elements rotated whole or not at all, rows aligned to a vector.
+    const bool whole = (rotary_dim == 0 || rotary_dim == head_dim) && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+                       projected_stride % (head_dim / 32) == 0;
+#define TAU_PREPARE_VEC(T, PER)                                                                                                     \
+    tau_launch(attention_prepare_vec_kernel<T, PER>, dim3(n_tokens), dim3(threads), 0, s, static_cast<const T*>(projected),          \
+               projected_stride, static_cast<T*>(queries), static_cast<T*>(keys), static_cast<T*>(values), q_weight, k_weight, eps,  \
+               cos_table, sin_table, rotary_dim, positions, token_seq, page_rows, page_stride, page_tokens, n_heads, n_kv_heads,     \
+               write_cache)
+    if (whole && dtype == TAU_BF16) {
+        if (head_dim == 64) TAU_PREPARE_VEC(bf16, 2);
+        else if (head_dim == 128) TAU_PREPARE_VEC(bf16, 4);
+        else TAU_PREPARE_VEC(bf16, 8);
+        return tau_launch_status();
+    }
+    if (whole && dtype == TAU_F32) {
+        if (head_dim == 64) TAU_PREPARE_VEC(float, 2);
+        else if (head_dim == 128) TAU_PREPARE_VEC(float, 4);
+        else TAU_PREPARE_VEC(float, 8);
+        return tau_launch_status();
+    }
+#undef TAU_PREPARE_VEC
     if (dtype == TAU_F32)
         tau_launch(attention_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, 
             static_cast<const float*>(projected), projected_stride, static_cast<float*>(queries), static_cast<float*>(keys),

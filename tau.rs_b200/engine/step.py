@@ -39,9 +39,16 @@ class Engine:
         self.cache = SequenceCache(model.cache_groups(), max_tokens, limit, model.dtype, self.device, max_slots)
         self._ring: Optional[PinnedRing] = None
         self._graphs: Dict = {}
+        self._split_choice: Dict = {}
         self.last_step_ints = 0     # size of the last step's metadata (int32 words copied to the device)
         # A captured step runs more than once while it is captured; state that a mixer updates in place forbids that.
         self.use_graphs = self.device.type == "cuda" and not self.cache.states
+
+    def ring(self, ints: int) -> PinnedRing:
+        """The pinned staging ring, grown if a step needs more room."""
+        if self._ring is None or self._ring.capacity < ints:
+            self._ring = PinnedRing(max(ints * 2, 1 << 16))
+        return self._ring
 
     # ---- sequences ---------------------------------------------------------------
     def open_sequence(self) -> int:
@@ -112,11 +119,10 @@ class Engine:
         if buffer is None:
             buffer = torch.empty(layout.total, dtype=torch.int32, device=self.device)
         if self.device.type == "cuda":
-            if self._ring is None or self._ring.capacity < layout.total:
-                self._ring = PinnedRing(max(layout.total * 2, 1 << 16))
-            staged, ticket = self._ring.acquire(layout.total)
+            ring = self.ring(layout.total)
+            staged, ticket = ring.acquire(layout.total)
             fill_step(layout, staged, entries, starts, self.cache)
-            self._ring.upload(ticket, layout.total, buffer)
+            ring.upload(ticket, layout.total, buffer)
         else:
             staged = np.zeros(layout.total, dtype=np.int32)
             fill_step(layout, staged, entries, starts, self.cache)

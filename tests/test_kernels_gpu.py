@@ -163,7 +163,8 @@ def paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed, pages=40
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,rotary_dim,with_norm", [
-    (4, 2, 16, 16, True), (6, 3, 48, 48, True), (8, 1, 32, 16, True), (3, 3, 128, 128, False), (2, 1, 256, 0, True)])
+    (4, 2, 16, 16, True), (6, 3, 48, 48, True), (8, 1, 32, 16, True), (3, 3, 128, 128, False), (2, 1, 256, 0, True),
+    (8, 2, 64, 64, True), (5, 1, 128, 128, True), (2, 2, 256, 256, True), (4, 2, 128, 64, True)])
 def test_attention_prepare(dtype, n_heads, n_kv_heads, head_dim, rotary_dim, with_norm):
     lengths, new_counts = [70, 5, 129], [70, 1, 3]
     keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=20)
