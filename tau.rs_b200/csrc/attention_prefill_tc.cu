@@ -1,0 +1,475 @@
+// Prefill attention on the fifth-generation tensor cores: bfloat16, causal, runs of new tokens over the paged cache.
+//
+// Compiled for one head size (-DTAU_HEAD_DIM=64 or 128).  The reference materialises the score matrix and an additive
+// mask (crates/models/src/components/gated_attention.rs:449-473); here a block owns 128 query positions of one head,
+// walks the keys in tiles of 64 (one cache page), and keeps both accumulators in tensor memory:
+//
+//   S = Q K^T     tcgen05.mma, A = Q tile and B = key tile from shared memory (both K-major, 128-byte swizzle, by TMA)
+//   softmax       four warps, one query row per thread: tcgen05.ld of the row, mask (`key <= query position`,
+//                 crates/models/src/qwen3_5_common/model.rs:154), running maximum and sum in 32-bit, probabilities
+//                 rounded to bfloat16 and written to shared memory in the swizzled K-major layout
+//   O += P V      tcgen05.mma, A = P from shared memory, B = value tile as it lies (`[key][d]`, MN-major)
+//
+// The accumulator O is rescaled only when a row's maximum has grown by more than 2^8 since the last rescale, so most
+// tiles do not touch it; the final division by the row sum makes the result exact either way.  Two blocks share an SM
+// (96 KB of shared memory and 256 columns of tensor memory each), so one block's softmax runs under the other's products.
+// Six warps: four for the softmax (one per 32-lane quarter of tensor memory), one TMA producer, one MMA issuer.  Every
+// mbarrier wait is bounded: after about two seconds the waiter raises an error flag, every role leaves its loop, tensor
+// memory is freed and the kernel returns (`tau_attention_prefill_tc_status`).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef TAU_HEAD_DIM
+#error "compile with -DTAU_HEAD_DIM=64 or 128"
+#endif
+
+namespace {
+
+constexpr int D = TAU_HEAD_DIM;
+static_assert(D == 64 || D == 128, "the tensor-core prefill kernel serves head sizes 64 and 128");
+constexpr int BM = 128;                 // query rows per block
+constexpr int BN = 64;                  // keys per tile: one cache page
+constexpr int kHalves = D / 64;         // 64-element (128-byte) slices of the head dimension
+constexpr int kThreads = 192;
+constexpr int kQBytes = BM * D * 2;
+constexpr int kKeyBytes = BN * D * 2;   // a key tile, or a value tile
+constexpr int kProbabilityBytes = BM * BN * 2;
+constexpr int kKeyAreaBytes = kKeyBytes > kProbabilityBytes ? kKeyBytes : kProbabilityBytes;   // the probabilities of a tile take the key tile's place
+constexpr int kStageBytes = kKeyAreaBytes + kKeyBytes;
+constexpr int kStages = 2;
+constexpr uint32_t kColumns = 256;      // S in columns [0, 64), O in columns [64, 64 + D)
+constexpr uint32_t kOColumn = 64;
+constexpr float kRescaleThreshold = 8.0f;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ int attention_tc_error = 0;
+
+__device__ __forceinline__ uint32_t smem_address(const void* pointer) { return static_cast<uint32_t>(__cvta_generic_to_shared(pointer)); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    return now;
+}
+
+__device__ __forceinline__ void barrier_init(uint64_t* barrier, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(barrier)), "r"(count));
+}
+__device__ __forceinline__ void barrier_expect_bytes(uint64_t* barrier, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(barrier)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void barrier_arrive(uint64_t* barrier) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+__device__ __forceinline__ bool barrier_try_wait(uint64_t* barrier, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_address(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Waits for the phase with the given parity to complete.  Returns false if the block is giving up.
+__device__ __forceinline__ bool barrier_wait(uint64_t* barrier, uint32_t parity, volatile int* abort_flag) {
+    if (barrier_try_wait(barrier, parity)) return true;
+    const unsigned long long started = global_timer();
+    for (uint32_t spin = 1;; ++spin) {
+        if (barrier_try_wait(barrier, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer() - started > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicExch(&attention_tc_error, 1);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* destination, const CUtensorMap* map, int inner, int outer, uint64_t* barrier) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_address(destination)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(inner), "r"(outer), "r"(smem_address(barrier))
+                 : "memory");
+}
+
+// K-major tile, rows of 128 bytes, 128-byte swizzle: groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t k_major_descriptor(uint32_t address) {
+    return static_cast<uint64_t>((address >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major tile (the value tile `[key][d]`): 128-byte rows hold 64 consecutive d of one key; groups of 8 keys are
+// 1024 bytes apart (stride offset); the next 64 d lie `kKeyBytes / kHalves` bytes further (leading offset).
+__device__ __forceinline__ uint64_t mn_major_descriptor(uint32_t address) {
+    constexpr uint64_t leading = (kKeyBytes / kHalves) >> 4;
+    return static_cast<uint64_t>((address >> 4) & 0x3fffu) | (leading << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// float accumulate, bfloat16 operands, M = 128, N = n; `b_mn_major` marks the B operand as MN-major.
+__device__ __forceinline__ uint32_t instruction_descriptor(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(BM >> 4) << 24);
+}
+__device__ __forceinline__ void mma_issue(uint32_t accumulator, uint64_t a, uint64_t b, uint32_t descriptor, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(accumulator), "l"(a), "l"(b), "r"(descriptor), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* barrier) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+__device__ __forceinline__ void tensor_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tensor_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tensor_load_32(uint32_t address, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(address));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tensor_store_32(uint32_t address, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(address), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ unsigned pack_bf16(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const unsigned*>(&pair);
+}
+
+struct Shared {
+    uint64_t q_full;
+    uint64_t kv_full[kStages];      // a key and value tile has landed
+    uint64_t stage_free[kStages];   // the products that read a stage have finished
+    uint64_t s_full;                // scores of a tile are in tensor memory
+    uint64_t s_free;                // the softmax has read them
+    uint64_t p_ready;               // probabilities of a tile are in shared memory (and O has been rescaled if need be)
+    uint64_t pv_done;               // the second product of a tile has finished
+    uint32_t tensor_memory_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                            const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ seq_start, const int* __restrict__ page_rows, int page_stride, int n_seqs,
+                            int n_heads, int n_kv_heads, float scale, int window) {
+    grid_dependents_launch();
+    extern __shared__ uint8_t shared_raw[];
+    Shared* shared = reinterpret_cast<Shared*>(shared_raw);
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_tile = tiles;                      // kHalves slices of [128 rows x 128 bytes]
+    uint8_t* stages = tiles + kQBytes;            // per stage: key tile (later the probabilities), value tile
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &shared->abort_flag;
+
+    if (threadIdx.x == 0) {
+        barrier_init(&shared->q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            barrier_init(&shared->kv_full[s], 1);
+            barrier_init(&shared->stage_free[s], 1);
+        }
+        barrier_init(&shared->s_full, 1);
+        barrier_init(&shared->s_free, 4);     // one arrival per softmax warp
+        barrier_init(&shared->p_ready, 4);
+        barrier_init(&shared->pv_done, 1);
+        shared->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(&shared->tensor_memory_base)),
+                     "r"(kColumns)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tensor_fence_before_sync();
+    __syncthreads();
+    tensor_fence_after_sync();
+    const uint32_t tensor_base = shared->tensor_memory_base;
+    grid_dependency_wait();
+
+    // Which sequence and which 128-row tile of it?  Blocks are numbered sequence by sequence, last tiles first.
+    int block = blockIdx.x, seq = 0, row0 = 0, n_new = 0;
+    for (; seq < n_seqs; ++seq) {
+        row0 = cu_seqlens[seq];
+        n_new = cu_seqlens[seq + 1] - row0;
+        const int blocks_here = (n_new + BM - 1) / BM;
+        if (block < blocks_here) {
+            block = blocks_here - 1 - block;
+            break;
+        }
+        block -= blocks_here;
+    }
+    const bool has_work = seq < n_seqs;
+    const int head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    const int start = has_work ? seq_start[seq] : 0;
+    const int rows_here = has_work ? min(BM, n_new - block * BM) : 0;
+    const int position0 = start + block * BM;                 // position of row 0
+    const int last_position = position0 + rows_here - 1;      // of the last real row
+    int first_key = 0;
+    if (window > 0 && position0 - window + 1 > 0) first_key = position0 - window + 1;
+    const int first_tile = first_key / BN;
+    const int n_tiles = has_work ? last_position / BN - first_tile + 1 : 0;
+    const int* pages = page_rows + static_cast<size_t>(has_work ? seq : 0) * page_stride;
+
+    if (warp == 4) {
+        // ---- producer -------------------------------------------------------------------------------------------
+        if (lane == 0 && has_work) {
+            barrier_expect_bytes(&shared->q_full, kQBytes);
+            for (int half = 0; half < kHalves; ++half)
+                tma_load_2d(q_tile + half * (BM * 128), &q_map, head * D + half * 64, row0 + block * BM, &shared->q_full);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % kStages;
+                const uint32_t use = i / kStages;
+                if (use > 0 && !barrier_wait(&shared->stage_free[s], (use - 1) & 1u, abort_flag)) break;
+                uint8_t* key_tile = stages + s * kStageBytes;
+                const int row = (pages[first_tile + i] * n_kv_heads + kv_head) * BN;
+                barrier_expect_bytes(&shared->kv_full[s], 2 * kKeyBytes);
+                for (int half = 0; half < kHalves; ++half) {
+                    tma_load_2d(key_tile + half * (BN * 128), &k_map, half * 64, row, &shared->kv_full[s]);
+                    tma_load_2d(key_tile + kKeyAreaBytes + half * (BN * 128), &v_map, half * 64, row, &shared->kv_full[s]);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issuer -----------------------------------------------------------------------------------------
+        if (lane == 0 && has_work) {
+            const uint32_t score_descriptor = instruction_descriptor(BN, false), value_descriptor = instruction_descriptor(D, true);
+            const uint32_t q_address = smem_address(q_tile);
+            bool alive = barrier_wait(&shared->q_full, 0, abort_flag);
+            for (int i = 0; i < n_tiles && alive; ++i) {
+                const int s = i % kStages;
+                const uint32_t key_address = smem_address(stages + s * kStageBytes), value_address = key_address + kKeyAreaBytes;
+                if (!barrier_wait(&shared->kv_full[s], (i / kStages) & 1u, abort_flag)) break;
+                // The softmax must have read the scores of the tile before (their first use needs no wait).
+                if (i > 0 && !barrier_wait(&shared->s_free, (i - 1) & 1u, abort_flag)) break;
+                tensor_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k) {
+                    const uint32_t offset = (k / 4) * 128 * BM + (k % 4) * 32;          // slice of 64 d, then 16 d inside it
+                    const uint32_t key_offset = (k / 4) * 128 * BN + (k % 4) * 32;
+                    mma_issue(tensor_base, k_major_descriptor(q_address + offset), k_major_descriptor(key_address + key_offset),
+                              score_descriptor, k > 0 ? 1u : 0u);
+                }
+                mma_commit(&shared->s_full);
+                // Probabilities lie where the key tile was.
+                if (!barrier_wait(&shared->p_ready, i & 1u, abort_flag)) break;
+                tensor_fence_after_sync();
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    mma_issue(tensor_base + kOColumn, k_major_descriptor(key_address + k * 32), mn_major_descriptor(value_address + k * 2048),
+                              value_descriptor, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                mma_commit(&shared->stage_free[s]);
+                mma_commit(&shared->pv_done);
+            }
+        }
+    } else if (has_work) {
+        // ---- softmax: thread = query row ----------------------------------------------------------------------------
+        const int row = warp * 32 + lane;                         // warp w may touch lanes 32 w .. 32 w + 31 of tensor memory
+        const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(warp * 32) << 16);
+        const int position = position0 + row;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        float used_max = -INFINITY, sum = 0.0f;                   // the maximum that O and `sum` are scaled by
+        bool alive = true;
+        for (int i = 0; i < n_tiles && alive; ++i) {
+            const int s = i % kStages;
+            if (!barrier_wait(&shared->s_full, i & 1u, abort_flag)) { alive = false; break; }
+            tensor_fence_after_sync();
+            float score[BN];
+            {
+                float part[32];
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    tensor_load_32(lane_base + c * 32, part);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) score[c * 32 + j] = part[j];
+                }
+            }
+            tensor_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&shared->s_free);
+            const int key0 = (first_tile + i) * BN;
+            if (key0 + BN - 1 > last_position) {
+                // Rows of the page beyond the last position hold whatever an earlier sequence left there.  Their
+                // probabilities are zero, but zero times a stale NaN is not: clear those value rows before the product.
+                uint8_t* value_tile = stages + s * kStageBytes + kKeyAreaBytes;
+                const int first_stale = last_position - key0 + 1;
+                for (int item = threadIdx.x; item < (BN - first_stale) * kHalves * 8; item += 128) {
+                    const int chunk = item % 8, half = (item / 8) % kHalves, stale_row = first_stale + item / (8 * kHalves);
+                    *reinterpret_cast<uint4*>(value_tile + half * (BN * 128) + stale_row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            const bool needs_mask = key0 + BN - 1 > position0 || (window > 0 && key0 <= position0 + BM - 1 - window);
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                float value = score[j] * scale_log2;
+                if (needs_mask) {
+                    const int key = key0 + j;
+                    const bool ok = key <= position && (window == 0 || key > position - window);
+                    value = ok ? value : -INFINITY;
+                }
+                score[j] = value;
+                tile_max = fmaxf(tile_max, value);
+            }
+            // Rescale O and the sum only when the maximum has grown by more than the threshold (or nothing was kept yet).
+            float shift = used_max;
+            const bool grow = tile_max > used_max + kRescaleThreshold;     // true for the first key a row sees
+            // O must not be touched while the second product of the tile before is still writing it.
+            if (i > 0 && !barrier_wait(&shared->pv_done, (i - 1) & 1u, abort_flag)) { alive = false; break; }
+            // The loads and stores of tensor memory are warp-wide, so the whole warp takes part if any of its rows grows.
+            const bool rescale = grow && i > 0 && used_max != -INFINITY;
+            if (__any_sync(0xffffffffu, rescale)) {
+                tensor_fence_after_sync();
+                const float factor = rescale ? exp2f(used_max - tile_max) : 1.0f;
+                sum *= factor;
+                float part[32];
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    tensor_load_32(lane_base + kOColumn + c * 32, part);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) part[j] *= factor;
+                    tensor_store_32(lane_base + kOColumn + c * 32, part);
+                }
+            }
+            if (grow) {
+                used_max = tile_max;
+                shift = tile_max;
+            }
+            const float subtract = shift == -INFINITY ? 0.0f : shift;   // a row that has seen no key yet
+            // Probabilities: row `row` of a [128 x 64] K-major tile, 16-byte chunk c at (c ^ (row % 8)).
+            uint8_t* p_row = stages + s * kStageBytes + row * 128;
+#pragma unroll
+            for (int c = 0; c < BN / 8; ++c) {
+                float p[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    p[j] = exp2f(score[c * 8 + j] - subtract);
+                    sum += p[j];
+                }
+                const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = packed;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
+            tensor_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) barrier_arrive(&shared->p_ready);
+        }
+        if (alive && n_tiles > 0 && barrier_wait(&shared->pv_done, (n_tiles - 1) & 1u, abort_flag)) {
+            tensor_fence_after_sync();
+            const float inverse = 1.0f / sum;
+            bf16* target = out + (static_cast<size_t>(row0 + block * BM + row) * n_heads + head) * D;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                float part[32];
+                tensor_load_32(lane_base + kOColumn + c * 32, part);   // every thread of the warp takes part in the load
+                if (row < rows_here) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        const uint4 packed = make_uint4(pack_bf16(part[j] * inverse, part[j + 1] * inverse), pack_bf16(part[j + 2] * inverse, part[j + 3] * inverse),
+                                                        pack_bf16(part[j + 4] * inverse, part[j + 5] * inverse), pack_bf16(part[j + 6] * inverse, part[j + 7] * inverse));
+                        *reinterpret_cast<uint4*>(target + c * 32 + j) = packed;
+                    }
+                }
+            }
+        }
+    }
+
+    tensor_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        tensor_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tensor_base), "r"(kColumns) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled function = nullptr;
+    if (!function) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            function = reinterpret_cast<EncodeTiled>(entry);
+    }
+    return function;
+}
+
+// A map over a row-major bfloat16 matrix `[rows, columns]`; boxes of `box_rows` rows by 64 columns (128 bytes), swizzled.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long columns, int box_rows) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(columns), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(columns) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_attention_prefill_tc_head_dim() { return D; }
+
+// 0 if no wait has run out since the library was loaded (synchronises the device).
+TAU_EXPORT int tau_attention_prefill_tc_status() {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, attention_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    return flag;
+}
+
+// `n_pages`: pages of the cache layer (keys and values are `[n_pages, n_kv_heads, 64, D]`).
+TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, const void* values, void* out, const int* cu_seqlens,
+                                        const int* seq_start, const int* page_rows, int page_stride, int page_tokens, long long n_pages,
+                                        int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, void* stream) {
+    if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (!queries || !keys || !values || !out || !cu_seqlens || !seq_start || !page_rows || n_heads <= 0 || n_kv_heads <= 0 ||
+        n_heads % n_kv_heads != 0 || page_tokens != BN || window < 0 || n_pages <= 0)
+        return cudaErrorInvalidValue;
+    CUtensorMap q_map, k_map, v_map;
+    const long long cache_rows = n_pages * n_kv_heads * BN;
+    if (!make_map(&q_map, queries, n_tokens, static_cast<long long>(n_heads) * D, BM) || !make_map(&k_map, keys, cache_rows, D, BN) ||
+        !make_map(&v_map, values, cache_rows, D, BN))
+        return cudaErrorInvalidValue;
+    const int shared_bytes = sizeof(Shared) + 1024 + kQBytes + kStages * kStageBytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        configured = true;
+    }
+    const int blocks = (n_tokens + BM - 1) / BM + n_seqs;   // every sequence may leave a ragged block
+    tau_launch(attention_prefill_tc_kernel, dim3(blocks, n_heads), dim3(kThreads), shared_bytes, static_cast<cudaStream_t>(stream), q_map,
+               k_map, v_map, static_cast<bf16*>(out), cu_seqlens, seq_start, page_rows, page_stride, n_seqs, n_heads, n_kv_heads, scale, window);
+    return tau_launch_status();
+}

@@ -400,6 +400,36 @@ def attention_prefill(queries, keys, values, out, cu_seqlens, seq_start, page_ro
         ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention_prefill")
 
 
+def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
+                         scale: float, window: int) -> None:
+    """The same as `attention_prefill` on the tcgen05 tensor cores (accumulators in tensor memory); head sizes 64 and 128."""
+    _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows)
+    tokens = queries.shape[0]
+    n_seqs = seq_start.numel()
+    _require(head_dim in (64, 128), "the tensor-core prefill kernel serves head sizes 64 and 128")
+    _require(queries.dtype == torch.bfloat16 == out.dtype == keys.dtype == values.dtype, "the tensor-core prefill kernel is bfloat16 only")
+    _require(queries.shape == (tokens, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.is_contiguous(),
+             "queries and output must be [tokens, n_heads * head_dim]")
+    _require(n_heads % n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads")
+    _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
+             and values.shape == keys.shape, "cache pages must be [pages, n_kv_heads, 64, head_dim]")
+    _int_vector(cu_seqlens, "cu_seqlens")
+    _int_vector(seq_start, "seq_start")
+    _require(cu_seqlens.numel() == n_seqs + 1 and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
+             and page_rows.shape[0] == n_seqs, "one run and one row of pages per sequence")
+    library = build.load_library("attention_prefill_tc.cu", (f"TAU_HEAD_DIM={head_dim}",))
+    _check(library.tau_attention_prefill_tc(
+        _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(cu_seqlens), _pointer(seq_start), _pointer(page_rows),
+        ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_longlong(keys.shape[0]), ctypes.c_int(n_seqs),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _stream()),
+        "attention_prefill_tc")
+
+
+def attention_prefill_tc_status(head_dim: int) -> int:
+    """0 unless a bounded wait inside the tensor-core prefill kernel ran out (synchronises the device)."""
+    return build.load_library("attention_prefill_tc.cu", (f"TAU_HEAD_DIM={head_dim}",)).tau_attention_prefill_tc_status()
+
+
 def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
               window: int) -> None:
     """Causal attention of the step's tokens over their sequences' cache pages (which hold the step's own keys already)."""
@@ -407,8 +437,8 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
         splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
         return attention_decode(queries, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits)
     if queries.dtype == torch.bfloat16:
-        return attention_prefill(queries, keys, values, out, step.cu_seqlens, step.seq_start, page_rows, n_heads, n_kv_heads, head_dim,
-                                 scale, window)
+        prefill = attention_prefill_tc if head_dim in (64, 128) else attention_prefill
+        return prefill(queries, keys, values, out, step.cu_seqlens, step.seq_start, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
 
 

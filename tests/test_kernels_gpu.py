@@ -246,6 +246,37 @@ def test_prefill_attention_kernel(n_heads, n_kv_heads, head_dim, window):
     close(found, wanted, dtype)
 
 
+@pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,window", [(8, 2, 128, 0), (4, 4, 64, 0), (6, 1, 128, 0), (4, 2, 128, 50), (2, 1, 64, 130)])
+def test_prefill_attention_tensor_memory_kernel(n_heads, n_kv_heads, head_dim, window):
+    """The tcgen05 prefill kernel: whole prompts, continued runs, ragged 128-row tiles, several pages, a window's edge,
+    a far key that must dominate; poisoned rows beyond each length must not be read into a result."""
+    dtype = torch.bfloat16
+    lengths, new_counts = [70, 200, 129, 1, 64, 700, 128], [70, 17, 129, 1, 33, 300, 128]
+    keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=90, pages=64)
+    tokens = positions.shape[0]
+    queries = randn(tokens, n_heads * head_dim, dtype=dtype, seed=91)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new_counts)]), dtype=torch.int32, device=DEVICE)
+    starts = torch.tensor([l - n for l, n in zip(lengths, new_counts)], dtype=torch.int32, device=DEVICE)
+    if window == 0:   # the last token of the longest request finds key 5 among 700
+        last = int(cu[6]) - 1
+        query = queries[last].view(n_heads, head_dim)[0].float()
+        keys[int(rows[5, 0]), 0, 5] = (query * 60.0 / query.norm()).to(dtype)
+    for index, length in enumerate(lengths):
+        for place in range(length, ((length + 63) // 64) * 64):
+            keys[int(rows[index, place // 64]), :, place % 64] = float("nan")
+            values[int(rows[index, place // 64]), :, place % 64] = float("nan")
+    found = torch.full_like(queries, float("nan"))
+    wanted = torch.empty(tokens, n_heads * head_dim, dtype=dtype)
+    kernels.attention_prefill_tc(queries, keys, values, found, cu, starts, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
+    close(found, wanted, dtype)
+    assert kernels.attention_prefill_tc_status(head_dim) == 0
+    if window == 0:
+        got = found[int(cu[6]) - 1].view(n_heads, head_dim)[0].float()
+        assert torch.allclose(got, values[int(rows[5, 0]), 0, 5].float(), atol=0.05, rtol=0.05)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim", [(4, 2, 16), (8, 2, 128), (6, 1, 80)])
 def test_decode_attention_finds_a_far_key(dtype, n_heads, n_kv_heads, head_dim):
