@@ -11,8 +11,11 @@
 //   O += P V      tcgen05.mma, A = P from shared memory, B = value tile as it lies (`[key][d]`, MN-major)
 //
 // The accumulator O is rescaled only when a row's maximum has grown by more than 2^8 since the last rescale, so most
-// tiles do not touch it; the final division by the row sum makes the result exact either way.  Two blocks share an SM
-// (96 KB of shared memory and 256 columns of tensor memory each), so one block's softmax runs under the other's products.
+// tiles do not touch it; the final division by the row sum makes the result exact either way.  The score products run
+// one tile ahead of the softmax (two score buffers in tensor memory), so the tensor cores work on tile i + 1 and on the
+// second product of tile i - 1 while the four warps are busy with tile i; two blocks share an SM (96 KB of shared memory
+// and 256 columns of tensor memory each) and fill each other's gaps.  Blocks are numbered with the heads fastest and the
+// last query tiles first, so that the tiles with the most keys start first on every head.
 // Six warps: four for the softmax (one per 32-lane quarter of tensor memory), one TMA producer, one MMA issuer.  Every
 // mbarrier wait is bounded: after about two seconds the waiter raises an error flag, every role leaves its loop, tensor
 // memory is freed and the kernel returns (`tau_attention_prefill_tc_status`).
@@ -37,9 +40,12 @@ constexpr int kKeyBytes = BN * D * 2;   // a key tile, or a value tile
 constexpr int kProbabilityBytes = BM * BN * 2;
 constexpr int kKeyAreaBytes = kKeyBytes > kProbabilityBytes ? kKeyBytes : kProbabilityBytes;   // the probabilities of a tile take the key tile's place
 constexpr int kStageBytes = kKeyAreaBytes + kKeyBytes;
-constexpr int kStages = 2;
-constexpr uint32_t kColumns = 256;      // S in columns [0, 64), O in columns [64, 64 + D)
-constexpr uint32_t kOColumn = 64;
+#ifndef TAU_ATTN_STAGES
+#define TAU_ATTN_STAGES 2
+#endif
+constexpr int kStages = TAU_ATTN_STAGES;          // 2: two blocks per SM (62 us for 2,048 tokens of 32 heads); 3: one block per SM (73 us)
+constexpr uint32_t kColumns = 256;      // two score buffers in columns [0, 64) and [64, 128), O in columns [128, 128 + D)
+constexpr uint32_t kOColumn = 128;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
@@ -66,10 +72,10 @@ __device__ __forceinline__ bool barrier_try_wait(uint64_t* barrier, uint32_t par
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"   // may sleep up to the hint before it answers
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(smem_address(barrier)), "r"(parity)
+        : "r"(smem_address(barrier)), "r"(parity), "r"(20000u)
         : "memory");
     return done != 0;
 }
@@ -126,6 +132,7 @@ __device__ __forceinline__ void mma_commit(uint64_t* barrier) {
 __device__ __forceinline__ void tensor_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tensor_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Starts a load of 32 columns of this thread's lane; see tensor_load_wait.
 __device__ __forceinline__ void tensor_load_32(uint32_t address, float (&v)[32]) {
     uint32_t r[32];
     asm volatile(
@@ -136,10 +143,11 @@ __device__ __forceinline__ void tensor_load_32(uint32_t address, float (&v)[32])
           "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The values of earlier tensor_load_32 calls may be used only after this.
+__device__ __forceinline__ void tensor_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tensor_store_32(uint32_t address, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
@@ -156,6 +164,13 @@ __device__ __forceinline__ void tensor_store_32(uint32_t address, const float (&
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 2^x on the special-function unit, one instruction (inputs here are <= 8 or -inf; tiny results may flush to zero).
+__device__ __forceinline__ float fast_exp2(float value) {
+    float result;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(result) : "f"(value));
+    return result;
+}
+
 __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
     const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<const unsigned*>(&pair);
@@ -164,16 +179,16 @@ __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
 struct Shared {
     uint64_t q_full;
     uint64_t kv_full[kStages];      // a key and value tile has landed
-    uint64_t stage_free[kStages];   // the products that read a stage have finished
-    uint64_t s_full;                // scores of a tile are in tensor memory
-    uint64_t s_free;                // the softmax has read them
-    uint64_t p_ready;               // probabilities of a tile are in shared memory (and O has been rescaled if need be)
+    uint64_t stage_free[kStages];   // the second product that read a stage has finished
+    uint64_t s_full[2];             // scores of a tile are in their buffer of tensor memory
+    uint64_t s_free[2];             // the softmax has read that buffer
+    uint64_t p_ready[2];            // probabilities of a tile are in shared memory (and O has been rescaled if need be)
     uint64_t pv_done;               // the second product of a tile has finished
     uint32_t tensor_memory_base;
     int abort_flag;
 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kStages == 2 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_start, const int* __restrict__ page_rows, int page_stride, int n_seqs,
@@ -193,9 +208,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             barrier_init(&shared->kv_full[s], 1);
             barrier_init(&shared->stage_free[s], 1);
         }
-        barrier_init(&shared->s_full, 1);
-        barrier_init(&shared->s_free, 4);     // one arrival per softmax warp
-        barrier_init(&shared->p_ready, 4);
+        for (int b = 0; b < 2; ++b) {
+            barrier_init(&shared->s_full[b], 1);
+            barrier_init(&shared->s_free[b], 4);     // one arrival per softmax warp
+            barrier_init(&shared->p_ready[b], 4);
+        }
         barrier_init(&shared->pv_done, 1);
         shared->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -213,7 +230,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     grid_dependency_wait();
 
     // Which sequence and which 128-row tile of it?  Blocks are numbered sequence by sequence, last tiles first.
-    int block = blockIdx.x, seq = 0, row0 = 0, n_new = 0;
+    int block = blockIdx.y, seq = 0, row0 = 0, n_new = 0;   // heads vary fastest, so the heaviest tiles of every head start first
     for (; seq < n_seqs; ++seq) {
         row0 = cu_seqlens[seq];
         n_new = cu_seqlens[seq + 1] - row0;
@@ -225,7 +242,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         block -= blocks_here;
     }
     const bool has_work = seq < n_seqs;
-    const int head = blockIdx.y, kv_head = head / (n_heads / n_kv_heads);
+    const int head = blockIdx.x, kv_head = head / (n_heads / n_kv_heads);
     const int start = has_work ? seq_start[seq] : 0;
     const int rows_here = has_work ? min(BM, n_new - block * BM) : 0;
     const int position0 = start + block * BM;                 // position of row 0
@@ -260,24 +277,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         if (lane == 0 && has_work) {
             const uint32_t score_descriptor = instruction_descriptor(BN, false), value_descriptor = instruction_descriptor(D, true);
             const uint32_t q_address = smem_address(q_tile);
-            bool alive = barrier_wait(&shared->q_full, 0, abort_flag);
-            for (int i = 0; i < n_tiles && alive; ++i) {
+            // Scores run one tile ahead of the softmax: while the four warps work on tile i, the products of tile i + 1
+            // fill the other score buffer, and the second product of tile i follows as soon as its probabilities are there.
+            auto issue_scores = [&](int i) {
                 const int s = i % kStages;
-                const uint32_t key_address = smem_address(stages + s * kStageBytes), value_address = key_address + kKeyAreaBytes;
-                if (!barrier_wait(&shared->kv_full[s], (i / kStages) & 1u, abort_flag)) break;
-                // The softmax must have read the scores of the tile before (their first use needs no wait).
-                if (i > 0 && !barrier_wait(&shared->s_free, (i - 1) & 1u, abort_flag)) break;
+                const uint32_t key_address = smem_address(stages + s * kStageBytes);
+                if (!barrier_wait(&shared->kv_full[s], (i / kStages) & 1u, abort_flag)) return false;
+                if (i >= 2 && !barrier_wait(&shared->s_free[i & 1], ((i >> 1) - 1) & 1u, abort_flag)) return false;
                 tensor_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < D / 16; ++k) {
                     const uint32_t offset = (k / 4) * 128 * BM + (k % 4) * 32;          // slice of 64 d, then 16 d inside it
                     const uint32_t key_offset = (k / 4) * 128 * BN + (k % 4) * 32;
-                    mma_issue(tensor_base, k_major_descriptor(q_address + offset), k_major_descriptor(key_address + key_offset),
-                              score_descriptor, k > 0 ? 1u : 0u);
+                    mma_issue(tensor_base + (i & 1) * BN, k_major_descriptor(q_address + offset),
+                              k_major_descriptor(key_address + key_offset), score_descriptor, k > 0 ? 1u : 0u);
                 }
-                mma_commit(&shared->s_full);
+                mma_commit(&shared->s_full[i & 1]);
+                return true;
+            };
+            bool alive = barrier_wait(&shared->q_full, 0, abort_flag) && issue_scores(0);
+            for (int i = 0; i < n_tiles && alive; ++i) {
+                if (i + 1 < n_tiles && !issue_scores(i + 1)) break;
+                const int s = i % kStages;
+                const uint32_t key_address = smem_address(stages + s * kStageBytes), value_address = key_address + kKeyAreaBytes;
                 // Probabilities lie where the key tile was.
-                if (!barrier_wait(&shared->p_ready, i & 1u, abort_flag)) break;
+                if (!barrier_wait(&shared->p_ready[i & 1], (i >> 1) & 1u, abort_flag)) break;
                 tensor_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
@@ -298,21 +322,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         bool alive = true;
         for (int i = 0; i < n_tiles && alive; ++i) {
             const int s = i % kStages;
-            if (!barrier_wait(&shared->s_full, i & 1u, abort_flag)) { alive = false; break; }
+            if (!barrier_wait(&shared->s_full[i & 1], (i >> 1) & 1u, abort_flag)) { alive = false; break; }
             tensor_fence_after_sync();
             float score[BN];
             {
-                float part[32];
+                float low[32], high[32];
+                tensor_load_32(lane_base + (i & 1) * BN, low);
+                tensor_load_32(lane_base + (i & 1) * BN + 32, high);
+                tensor_load_wait();
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
-                    tensor_load_32(lane_base + c * 32, part);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) score[c * 32 + j] = part[j];
+                for (int j = 0; j < 32; ++j) {
+                    score[j] = low[j];
+                    score[32 + j] = high[j];
                 }
             }
             tensor_fence_before_sync();
             __syncwarp();
-            if (lane == 0) barrier_arrive(&shared->s_free);
+            if (lane == 0) barrier_arrive(&shared->s_free[i & 1]);
             const int key0 = (first_tile + i) * BN;
             if (key0 + BN - 1 > last_position) {
                 // Rows of the page beyond the last position hold whatever an earlier sequence left there.  Their
@@ -325,18 +351,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 }
             }
             const bool needs_mask = key0 + BN - 1 > position0 || (window > 0 && key0 <= position0 + BM - 1 - window);
-            float tile_max = -INFINITY;
+            if (needs_mask) {   // a diagonal tile (or a window's edge): keys [lowest, highest] of the tile are visible to this row
+                const int highest = position - key0, lowest = window > 0 ? position - window + 1 - key0 : 0;
 #pragma unroll
-            for (int j = 0; j < BN; ++j) {
-                float value = score[j] * scale_log2;
-                if (needs_mask) {
-                    const int key = key0 + j;
-                    const bool ok = key <= position && (window == 0 || key > position - window);
-                    value = ok ? value : -INFINITY;
-                }
-                score[j] = value;
-                tile_max = fmaxf(tile_max, value);
+                for (int j = 0; j < BN; ++j) score[j] = (j <= highest && j >= lowest) ? score[j] : -INFINITY;
             }
+            float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < BN; ++j) partial_max[j & 3] = fmaxf(partial_max[j & 3], score[j]);
+            // Of the raw scores; the scale is positive and is applied afterwards.
+            float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
+            tile_max *= scale_log2;
             // Rescale O and the sum only when the maximum has grown by more than the threshold (or nothing was kept yet).
             float shift = used_max;
             const bool grow = tile_max > used_max + kRescaleThreshold;     // true for the first key a row sees
@@ -352,6 +377,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     tensor_load_32(lane_base + kOColumn + c * 32, part);
+                    tensor_load_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) part[j] *= factor;
                     tensor_store_32(lane_base + kOColumn + c * 32, part);
@@ -364,21 +390,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             const float subtract = shift == -INFINITY ? 0.0f : shift;   // a row that has seen no key yet
             // Probabilities: row `row` of a [128 x 64] K-major tile, 16-byte chunk c at (c ^ (row % 8)).
             uint8_t* p_row = stages + s * kStageBytes + row * 128;
+            float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < BN / 8; ++c) {
                 float p[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    p[j] = exp2f(score[c * 8 + j] - subtract);
-                    sum += p[j];
+                    p[j] = fast_exp2(fmaf(score[c * 8 + j], scale_log2, -subtract));
+                    partial_sum[j & 3] += p[j];
                 }
                 const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
                 *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = packed;
             }
+            sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
             tensor_fence_before_sync();
             __syncwarp();
-            if (lane == 0) barrier_arrive(&shared->p_ready);
+            if (lane == 0) barrier_arrive(&shared->p_ready[i & 1]);
         }
         if (alive && n_tiles > 0 && barrier_wait(&shared->pv_done, (n_tiles - 1) & 1u, abort_flag)) {
             tensor_fence_after_sync();
@@ -388,6 +416,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             for (int c = 0; c < D / 32; ++c) {
                 float part[32];
                 tensor_load_32(lane_base + kOColumn + c * 32, part);   // every thread of the warp takes part in the load
+                tensor_load_wait();
                 if (row < rows_here) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
@@ -469,7 +498,7 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
         configured = true;
     }
     const int blocks = (n_tokens + BM - 1) / BM + n_seqs;   // every sequence may leave a ragged block
-    tau_launch(attention_prefill_tc_kernel, dim3(blocks, n_heads), dim3(kThreads), shared_bytes, static_cast<cudaStream_t>(stream), q_map,
+    tau_launch(attention_prefill_tc_kernel, dim3(n_heads, blocks), dim3(kThreads), shared_bytes, static_cast<cudaStream_t>(stream), q_map,
                k_map, v_map, static_cast<bf16*>(out), cu_seqlens, seq_start, page_rows, page_stride, n_seqs, n_heads, n_kv_heads, scale, window);
     return tau_launch_status();
 }
