@@ -51,7 +51,8 @@ __device__ __forceinline__ void copy_async_16(void* destination, const void* sou
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int NB, typename TOut>
+// `Gated`: a block's 16 rows are 8 gate rows followed by their 8 up rows; it writes silu(gate) * up to `out[M, N / 2]`.
+template <int NB, typename TOut, bool Gated>
 __global__ void __launch_bounds__(kWarps * 32, TAU_SKINNY_MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias, TOut* __restrict__ out,
                    int M, int N, int K, long long x_stride, long long w_stride, long long out_stride) {
@@ -141,31 +142,38 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     for (int index = threadIdx.x; index < NB * 8 * kRows; index += kWarps * 32) {
         const int token = index / kRows, r = index % kRows;
         const int feature = row0 + r;
-        if (token >= M || feature >= N) continue;
         float sum = 0.0f;
 #pragma unroll
         for (int wi = 0; wi < kWarps; ++wi) sum += partial[wi][token][r];
-        if (bias) sum += bias[feature];
-        out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(sum);
+        if (bias && feature < N) sum += bias[feature];
+        if (Gated) {
+            // Threads r and r ^ 8 of the same 16 hold a gate and its up value; both are rounded as the unfused product would store them.
+            const float mine = round_through<bf16>(sum);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+            if (r < 8 && token < M && feature < N)
+                out[static_cast<size_t>(token) * out_stride + (row0 >> 1) + r] = from_float<TOut>(mine / (1.0f + expf(-mine)) * other);
+        } else if (token < M && feature < N) {
+            out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(sum);
+        }
     }
 }
 
-template <int NB>
+template <int NB, bool Gated>
 int launch(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride,
            long long w_stride, long long out_stride, cudaStream_t stream) {
     const unsigned blocks = (N + kRows - 1) / kRows;
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-        if (status == cudaSuccess) status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        cudaError_t status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, bf16, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
+        if (status == cudaSuccess) status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, float, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
         if (status != cudaSuccess) return static_cast<int>(status);
         configured = true;
     }
     if (out_dtype == TAU_BF16)
-        tau_launch(gemm_skinny_kernel<NB, bf16>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, bf16, Gated>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                         static_cast<bf16*>(out), M, N, K, x_stride, w_stride, out_stride);
     else
-        tau_launch(gemm_skinny_kernel<NB, float>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
+        tau_launch(gemm_skinny_kernel<NB, float, Gated>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
                                                                          static_cast<float*>(out), M, N, K, x_stride, w_stride, out_stride);
     return tau_launch_status();
 }
@@ -176,14 +184,19 @@ TAU_EXPORT int tau_gemm_skinny_max_rows() { return 32; }
 
 // bfloat16 inputs; `out_dtype` bfloat16 or float32.  Strides in elements.
 TAU_EXPORT int tau_gemm_skinny(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                               long long x_stride, long long w_stride, long long out_stride, void* stream) {
+                               long long x_stride, long long w_stride, long long out_stride, int gated, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out || K <= 0 || M > 32 || (K & 7) || (x_stride & 7) || (w_stride & 7) ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-        (out_dtype != TAU_BF16 && out_dtype != TAU_F32))
+        (out_dtype != TAU_BF16 && out_dtype != TAU_F32) || (gated && (N & 15)))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (M <= 8) return launch<1>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
-    if (M <= 16) return launch<2>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
-    return launch<4>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+    if (gated) {
+        if (M <= 8) return launch<1, true>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+        if (M <= 16) return launch<2, true>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+        return launch<4, true>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+    }
+    if (M <= 8) return launch<1, false>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+    if (M <= 16) return launch<2, false>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
+    return launch<4, false>(out_dtype, x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, s);
 }

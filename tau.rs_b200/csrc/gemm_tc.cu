@@ -137,7 +137,9 @@ struct Shared {
     int abort_flag;
 };
 
-template <int BN, typename TOut>
+// `Gated`: the weight's rows come in groups of 16, 8 gate rows followed by their 8 up rows; the epilogue writes
+// silu(gate) * up, so `out` has N / 2 columns (crates/cuda-kernels/src/kernels/silu_and_mul.cu:51-76 as an epilogue).
+template <int BN, typename TOut, bool Gated>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
                const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
@@ -240,7 +242,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
             for (int chunk = 0; chunk < BN; chunk += 16) {
                 uint32_t v[16];
                 tensor_load_16(lane_base + chunk, v);
-                if (feature < N) {
+                if (Gated) {
+                    // Lanes 0-7 of each 16 hold gate rows, lanes 8-15 the matching up rows: bring them together.
+                    const int out_feature = (feature >> 4) * 8 + (feature & 7);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        // Both are rounded to the storage type first, as the unfused product would have stored them.
+                        const float mine = round_through<bf16>(__uint_as_float(v[j]) + offset);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                        const int token = token0 + chunk + j;
+                        if ((lane & 8) == 0 && feature < N && token < M)
+                            out[static_cast<size_t>(token) * out_stride + out_feature] = from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);   // the result is rounded to bfloat16: the fast forms lose nothing
+                    }
+                } else if (feature < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int token = token0 + chunk + j;
@@ -303,7 +317,7 @@ int sm_count() {
     return count;
 }
 
-template <int BN, typename TOut>
+template <int BN, typename TOut, bool Gated>
 int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const float* bias, void* out, int M, int N, int K,
            long long out_stride, cudaStream_t stream) {
     constexpr int stage_bytes = (BM + BN) * BK * 2;
@@ -312,26 +326,26 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
     const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
         if (status != cudaSuccess) return static_cast<int>(status);
         configured = true;
     }
     const int tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
     const int blocks = tiles < sm_count() ? tiles : sm_count();
-    tau_launch(gemm_tc_kernel<BN, TOut>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
+    tau_launch(gemm_tc_kernel<BN, TOut, Gated>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
                                                                          out_stride, stages);
     return tau_launch_status();
 }
 
-template <typename TOut>
+template <typename TOut, bool Gated>
 int dispatch(const CUtensorMap& weight_map, const CUtensorMap& input_map, int box, const float* bias, void* out, int M, int N, int K,
              long long out_stride, cudaStream_t stream) {
     switch (box) {
-        case 16: return launch<16, TOut>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 32: return launch<32, TOut>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 64: return launch<64, TOut>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 128: return launch<128, TOut>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        default: return launch<256, TOut>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        case 16: return launch<16, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        case 32: return launch<32, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        case 64: return launch<64, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        case 128: return launch<128, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        default: return launch<256, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
     }
 }
 
@@ -345,8 +359,9 @@ TAU_EXPORT int tau_gemm_tc_status() {
 }
 
 // bfloat16 inputs; `out_dtype` bfloat16 or float32.  Strides in elements.  `token_box` = 0 picks the token tile from M.
+// `gated`: rows of `w` are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
 TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                           long long x_stride, long long w_stride, long long out_stride, int token_box, void* stream) {
+                           long long x_stride, long long w_stride, long long out_stride, int token_box, int gated, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out || K <= 0 || (K & 7) || (x_stride & 7) || (w_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) ||
         (reinterpret_cast<uintptr_t>(w) & 15) || (out_dtype != TAU_BF16 && out_dtype != TAU_F32))
@@ -357,6 +372,7 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     CUtensorMap weight_map, input_map;
     if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, box)) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (out_dtype == TAU_BF16) return dispatch<bf16>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
-    return dispatch<float>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
+    if (gated) return dispatch<bf16, true>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
+    if (out_dtype == TAU_BF16) return dispatch<bf16, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
+    return dispatch<float, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
 }

@@ -164,12 +164,16 @@ def _skinny_fits(values, weight, out) -> bool:
             and weight.data_ptr() % 16 == 0)
 
 
-def gemm_skinny(values, weight, bias, out) -> None:
-    """bfloat16 product for at most 32 activation rows, bound by streaming `weight` once."""
+def gemm_skinny(values, weight, bias, out, gated: bool = False) -> None:
+    """bfloat16 product for at most 32 activation rows, bound by streaming `weight` once.
+
+    `gated`: the weight's rows are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
+    """
     _on_device(values, weight, bias, out)
     rows, depth = values.shape
     features = weight.shape[0]
-    _require(weight.shape[1] == depth and out.shape == (rows, features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(weight.shape[1] == depth and out.shape == (rows, features // 2 if gated else features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(not gated or features % 16 == 0, "a gated product needs a multiple of 16 weight rows")
     _require(values.dtype == weight.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32),
              "inputs must be bfloat16 and the output bfloat16 or float32")
     _require(_skinny_fits(values, weight, out), "needs M <= 32, K % 8 == 0 and 16-byte aligned rows")
@@ -177,7 +181,8 @@ def gemm_skinny(values, weight, bias, out) -> None:
     library = build.load_library("gemm_skinny.cu")
     _check(library.tau_gemm_skinny(_code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out), ctypes.c_int(rows),
                                    ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
-                                   ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), _stream()), "gemm_skinny")
+                                   ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(1 if gated else 0),
+                                   _stream()), "gemm_skinny")
 
 
 def _tc_fits(values, weight, out) -> bool:
@@ -185,12 +190,16 @@ def _tc_fits(values, weight, out) -> bool:
             and values.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_tc(values, weight, bias, out, token_box: int = 0) -> None:
-    """bfloat16 product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); any M and N, K % 8 == 0."""
+def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False) -> None:
+    """bfloat16 product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); any M and N, K % 8 == 0.
+
+    `gated`: the weight's rows are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
+    """
     _on_device(values, weight, bias, out)
     rows, depth = values.shape
     features = weight.shape[0]
-    _require(weight.shape[1] == depth and out.shape == (rows, features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(weight.shape[1] == depth and out.shape == (rows, features // 2 if gated else features), "shapes must be [M,K] x [N,K] -> [M,N]")
+    _require(not gated or (features % 16 == 0 and out.dtype == torch.bfloat16), "a gated product needs a multiple of 16 weight rows and a bfloat16 output")
     _require(values.dtype == weight.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32),
              "inputs must be bfloat16 and the output bfloat16 or float32")
     _require(_tc_fits(values, weight, out), "needs K % 8 == 0 and 16-byte aligned rows")
@@ -198,8 +207,8 @@ def gemm_tc(values, weight, bias, out, token_box: int = 0) -> None:
     library = build.load_library("gemm_tc.cu")
     _check(library.tau_gemm_tc(_code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out), ctypes.c_int(rows),
                                ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
-                               ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box), _stream()),
-           "gemm_tc")
+                               ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box),
+                               ctypes.c_int(1 if gated else 0), _stream()), "gemm_tc")
 
 
 def gemm_tc_status() -> int:
@@ -215,6 +224,23 @@ def gemm_library(values, weight, bias, out) -> None:
     torch.mm(values, weight.t(), out=out)
     if bias is not None:
         out.add_(bias.to(out.dtype))
+
+
+GATE_GROUP = 8   # rows of a gate (and of its up) that lie together in a weight prepared for `linear_gated`
+
+
+def gated_fits(in_features: int, out_features: int, dtype) -> bool:
+    """Whether `linear_gated` serves a gate/up pair of these sizes (else: `linear`, then `silu_mul`)."""
+    return dtype == torch.bfloat16 and in_features % 8 == 0 and out_features % GATE_GROUP == 0
+
+
+def linear_gated(values, weight, out) -> None:
+    """`out = silu(values @ gate.T) * (values @ up.T)` in one product; `weight` holds groups of 8 gate rows followed by
+    their 8 up rows (see `parts.linear.StackedLinear(interleave=...)`)."""
+    if _skinny_fits(values, weight, out):
+        return gemm_skinny(values, weight, None, out, gated=True)
+    _require(_tc_fits(values, weight, out), "the gated product needs bfloat16, K % 8 == 0 and 16-byte aligned rows")
+    gemm_tc(values, weight, None, out, gated=True)
 
 
 def linear(values, weight, bias, out) -> None:

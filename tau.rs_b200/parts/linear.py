@@ -23,7 +23,10 @@ class StackedLinear(Part):
     `<prefix>.bias` if `bias`) are stacked along the output axis in that order.
     """
 
-    def __init__(self, pieces: Sequence[Tuple[str, int]], in_features: int, bias: bool, dtype, device):
+    def __init__(self, pieces: Sequence[Tuple[str, int]], in_features: int, bias: bool, dtype, device, interleave: int = 0):
+        """`interleave` > 0 (two pieces of equal size, no bias): rows are stored in groups of `interleave` rows of the
+        first piece followed by the matching rows of the second, which is what a gated product reads."""
+        self.interleave = interleave
         self.pieces = list(pieces)
         self.in_features = in_features
         self.out_features = sum(width for _, width in self.pieces)
@@ -48,11 +51,22 @@ class StackedLinear(Part):
 
     def finalize_weights(self):
         weights = [self._parts.pop(f"{prefix}.weight") for prefix, _ in self.pieces]
-        self.weight = weights[0] if len(weights) == 1 else torch.cat(weights, dim=0).contiguous()
+        if self.interleave:
+            first, second = weights
+            group, width = self.interleave, first.shape[1]
+            self.weight = torch.stack([first.view(-1, group, width), second.view(-1, group, width)], dim=1).reshape(-1, width).contiguous()
+        else:
+            self.weight = weights[0] if len(weights) == 1 else torch.cat(weights, dim=0).contiguous()
         del weights
         if self.has_bias:
             biases = [self._parts.pop(f"{prefix}.bias") for prefix, _ in self.pieces]
             self.bias = biases[0] if len(biases) == 1 else torch.cat(biases, dim=0).contiguous()
+
+    def forward_gated(self, values):
+        """`silu(first piece) * second piece`, for a stack built with `interleave`."""
+        out = torch.empty((values.shape[0], self.out_features // 2), dtype=values.dtype, device=values.device)
+        kernels.linear_gated(values, self.weight, out)
+        return out
 
     def forward(self, values, out_dtype=None, rows: Optional[int] = None):
         """`rows` limits the product to the first `rows` output features (a prefix of the stack)."""

@@ -19,9 +19,12 @@ from .registry import register_feed_forward
 class SwiGLU(FeedForward):
     def __init__(self, spec, prefix: str, dtype, device):
         self.spec = spec
+        # Where the gated product exists (bfloat16, aligned sizes) gate and up rows are interleaved for it and the
+        # activation is its epilogue; otherwise the two are stacked and the activation is a kernel of its own.
+        self.fused = kernels.gated_fits(spec.hidden, spec.intermediate, dtype)
         self.gate_up = StackedLinear(
             [(f"{prefix}.gate_proj", spec.intermediate), (f"{prefix}.up_proj", spec.intermediate)],
-            spec.hidden, False, dtype, device,
+            spec.hidden, False, dtype, device, interleave=kernels.GATE_GROUP if self.fused else 0,
         )
         self.down = StackedLinear([(f"{prefix}.down_proj", spec.hidden)], spec.intermediate, False, dtype, device)
 
@@ -37,6 +40,8 @@ class SwiGLU(FeedForward):
         self.down.finalize_weights()
 
     def forward(self, hidden, step):
+        if self.fused:
+            return self.down.forward(self.gate_up.forward_gated(hidden))
         stacked = self.gate_up.forward(hidden)
         activated = torch.empty((hidden.shape[0], self.spec.intermediate), dtype=hidden.dtype, device=hidden.device)
         kernels.silu_mul(stacked, activated)

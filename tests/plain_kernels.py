@@ -51,6 +51,23 @@ def linear(values, weight, bias, out):
 
 
 gemm_simt = linear
+GATE_GROUP = 8
+
+
+def gated_fits(in_features, out_features, dtype):
+    return False     # the host-logic tests keep the product and the activation apart
+
+
+def linear_gated(values, weight, out):
+    """Rows of `weight`: groups of 8 gate rows followed by their 8 up rows."""
+    width = weight.shape[1]
+    grouped = weight.view(-1, 2, GATE_GROUP, width)
+    gate, up = grouped[:, 0].reshape(-1, width), grouped[:, 1].reshape(-1, width)
+    g = torch.empty(values.shape[0], gate.shape[0], dtype=values.dtype)
+    u = torch.empty_like(g)
+    linear(values, gate, None, g)
+    linear(values, up, None, u)
+    silu_mul(torch.cat([g, u], dim=1), out)
 
 
 def _page_offsets(page_rows, token_seq, positions):
@@ -174,7 +191,7 @@ def sample_gumbel(logits, tokens, valid, inverse_temperature, seed, request_ids,
         tokens[row], valid[row] = token, ok
 
 
-ALL = ("embedding", "rms_norm", "add_rms_norm", "silu_mul", "linear", "gemm_simt", "attention_prepare", "attention_generic",
+ALL = ("embedding", "rms_norm", "add_rms_norm", "silu_mul", "linear", "gemm_simt", "gated_fits", "linear_gated", "attention_prepare", "attention_generic",
        "attention", "attention_decode_fused", "decode_splits", "argmax", "sample_gumbel")
 
 

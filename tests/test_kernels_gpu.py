@@ -124,6 +124,22 @@ def test_gemm_tc(out_dtype, m, n, k, box):
     assert kernels.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 16, 8), (8, 48, 72), (20, 240, 200), (32, 1000 // 16 * 16, 64), (33, 64, 136), (200, 400, 96), (300, 16, 520)])
+def test_gated_products(m, n, k):
+    """silu(gate) * up as the epilogue of the skinny and of the tcgen05 product, on interleaved gate/up rows."""
+    values = randn(m, k, dtype=torch.bfloat16, seed=21)
+    weight = randn(n, k, dtype=torch.bfloat16, seed=22)
+    wanted = torch.empty(m, n // 2, dtype=torch.bfloat16)
+    plain_kernels.linear_gated(values.cpu(), weight.cpu(), wanted)
+    found = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+    kernels.linear_gated(values, weight, found)
+    close(found, wanted, torch.bfloat16)
+    found.fill_(float("nan"))
+    kernels.gemm_tc(values, weight, None, found, gated=True)
+    close(found, wanted, torch.bfloat16)
+    assert kernels.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_linear_dispatch_matches_plain(dtype):
     """Whatever kernel `linear` picks for a shape, the product is the same: ragged and aligned shapes, views of a stack."""
