@@ -69,10 +69,10 @@ static inline bool tau_dependent_launch_enabled() {
     return enabled;
 }
 
-// Launches `kernel` so that it may begin before the previous kernel of the stream has finished.
+// Launches `kernel`; with `dependent` it may begin before the previous kernel of the stream has finished.
 template <typename... Parameters, typename... Arguments>
-static inline int tau_launch(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
-                             Arguments&&... arguments) {
+static inline int tau_launch_as(bool dependent, void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                                Arguments&&... arguments) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -82,8 +82,15 @@ static inline int tau_launch(void (*kernel)(Parameters...), dim3 grid, dim3 bloc
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = tau_dependent_launch_enabled() ? 1 : 0;
+    config.numAttrs = (dependent && tau_dependent_launch_enabled()) ? 1 : 0;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, Parameters(std::forward<Arguments>(arguments))...));
+}
+
+// Launches `kernel` so that it may begin before the previous kernel of the stream has finished.
+template <typename... Parameters, typename... Arguments>
+static inline int tau_launch(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                             Arguments&&... arguments) {
+    return tau_launch_as(true, kernel, grid, block, shared_bytes, stream, std::forward<Arguments>(arguments)...);
 }
 
 TAU_EXPORT const char* tau_error_string(int code);

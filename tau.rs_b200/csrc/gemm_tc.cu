@@ -17,6 +17,11 @@
 // products of the next.  Every wait on an mbarrier is bounded: after about two seconds the waiter raises
 // an error flag, every role leaves its loop, tensor memory is freed and the kernel returns.
 //
+// With few tiles (a decode batch of 64 has 32 tiles of the output projection for 148 SMs) the work is also cut
+// along K: a work item is (tile, K range), each item leaves its float partial tile in a workspace, and the
+// epilogue warp that arrives last at a (tile, quarter) ticket adds the partials in the order of the ranges, so
+// the sum does not depend on who finishes last, and stores the result.  No block waits for another.
+//
 // Needs K % 8 == 0 and 16-byte aligned rows (TMA strides); other shapes go to the plain tiled kernel.
 #include <cuda.h>
 
@@ -27,8 +32,15 @@ namespace {
 constexpr int BM = 128;        // features per tile
 constexpr int BK = 64;         // K elements per stage: 128 bytes, one swizzle row
 constexpr int kMmaK = 16;      // K of one tcgen05.mma for 16-bit inputs
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;        // producer, issuer, four epilogue warps
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+#ifndef TAU_TC_ROTATE
+#define TAU_TC_ROTATE 0
+#endif
+
+// Where in its K range an item starts (it wraps around): items that run side by side then read different columns
+// of the weight at any moment instead of all the same one.
+__device__ __forceinline__ int first_block(int item, int count) { return TAU_TC_ROTATE ? (item * TAU_TC_ROTATE) % count : 0; }
 
 __device__ int gemm_tc_error = 0;   // raised when a wait ran out; read by tau_gemm_tc_status
 
@@ -140,9 +152,10 @@ struct Shared {
 // `Gated`: the weight's rows come in groups of 16, 8 gate rows followed by their 8 up rows; the epilogue writes
 // silu(gate) * up, so `out` has N / 2 columns (crates/cuda-kernels/src/kernels/silu_and_mul.cu:51-76 as an epilogue).
 template <int BN, typename TOut, bool Gated>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, BN <= 128 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
-               const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
+               const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages,
+               int splits, float* __restrict__ workspace, int* __restrict__ tickets) {
     grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
@@ -152,7 +165,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature_tiles = (N + BM - 1) / BM, token_tiles = (M + BN - 1) / BN;
-    const int n_tiles = feature_tiles * token_tiles;
+    const int n_items = feature_tiles * token_tiles * splits;   // item = tile * splits + K range
     const int k_blocks = (K + BK - 1) / BK;
     volatile int* abort_flag = &shared->abort_flag;
 
@@ -178,24 +191,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     __syncthreads();
     tensor_fence_after_sync();
     const uint32_t tensor_base = shared->tensor_memory_base;
-    grid_dependency_wait();   // barriers and tensor memory were set up while the previous kernel was finishing
+    // Barriers and tensor memory were set up while the previous kernel was finishing.  Each role waits for that kernel
+    // only before it touches what that kernel may write or read: the inputs (producer) and the output (epilogue).
 
     if (warp == 0) {
         // ---- producer: TMA loads of the weight and input tiles of each stage --------------------------
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+            // The weight never depends on the previous kernel: until every stage is in use, only weight tiles are asked
+            // for; then the producer waits for the previous kernel and sends the input tiles of those stages after them.
+            bool waited = false;
+            int held = 0, held_k[8], held_token[8];
+            auto release = [&]() {
+                grid_dependency_wait();
+                waited = true;
+                for (int h = 0; h < held; ++h)
+                    tma_load_2d(tiles + h * kStageBytes + kWeightBytes, &input_map, held_k[h], held_token[h], &shared->full[h]);
+            };
+            for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+                const int tile = item / splits, split = item - tile * splits;
                 const int feature0 = (tile / token_tiles) * BM, token0 = (tile % token_tiles) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                const int kb_begin = k_blocks * split / splits, count = k_blocks * (split + 1) / splits - kb_begin;
+                const int shift = first_block(item, count);
+                for (int i = 0; i < count; ++i) {
+                    const int kb = kb_begin + (i + shift < count ? i + shift : i + shift - count);
+                    if (!waited && held == stages) release();
                     if (!barrier_wait(&shared->empty[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
                     uint8_t* weight_tile = tiles + stage * kStageBytes;
                     barrier_expect_bytes(&shared->full[stage], kStageBytes);
                     tma_load_2d(weight_tile, &weight_map, kb * BK, feature0, &shared->full[stage]);
-                    tma_load_2d(weight_tile + kWeightBytes, &input_map, kb * BK, token0, &shared->full[stage]);
+                    if (waited) {
+                        tma_load_2d(weight_tile + kWeightBytes, &input_map, kb * BK, token0, &shared->full[stage]);
+                    } else {   // the first `stages` loads: stage == held
+                        held_k[held] = kb * BK;
+                        held_token[held] = token0;
+                        ++held;
+                    }
                     if (++stage == static_cast<uint32_t>(stages)) { stage = 0; phase ^= 1u; }
                 }
             }
+            if (!waited) release();
         }
     } else if (warp == 1) {
         // ---- MMA issuer ---------------------------------------------------------------------------------
@@ -203,13 +239,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
             const uint32_t descriptor = instruction_descriptor(BN);
             uint32_t stage = 0, phase = 0, local = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+            for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++local) {
                 const uint32_t slot = local & 1u, use = local >> 1;
+                const int split = item % splits;
+                const int kb_begin = k_blocks * split / splits, kb_end = k_blocks * (split + 1) / splits;
                 // The epilogue must have drained this accumulator (its first use needs no wait).
                 if (use > 0 && !barrier_wait(&shared->accumulator_empty[slot], (use - 1) & 1u, abort_flag)) { alive = false; break; }
                 tensor_fence_after_sync();
                 const uint32_t accumulator = tensor_base + slot * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {   // the producer decides which K block a stage holds
                     if (!barrier_wait(&shared->full[stage], phase, abort_flag)) { alive = false; break; }
                     tensor_fence_after_sync();
                     const uint32_t weight_address = smem_address(tiles + stage * kStageBytes);
@@ -217,7 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BK / kMmaK; ++k) {
                         mma_issue(accumulator, tile_descriptor(weight_address + k * kMmaK * 2), tile_descriptor(input_address + k * kMmaK * 2),
-                                  descriptor, (kb > 0 || k > 0) ? 1u : 0u);
+                                  descriptor, (kb > kb_begin || k > 0) ? 1u : 0u);
                     }
                     mma_commit(&shared->empty[stage]);   // the stage is free once these products have read it
                     if (++stage == static_cast<uint32_t>(stages)) { stage = 0; phase ^= 1u; }
@@ -230,41 +268,115 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
         const int quarter = warp & 3;
         uint32_t local = 0;
         bool alive = true;
-        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+        grid_dependency_wait();   // the output, the workspace and the tickets may still be in use by the previous kernel
+        for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++local) {
             const uint32_t slot = local & 1u, use = local >> 1;
+            const int tile = item / splits;
             const int feature = (tile / token_tiles) * BM + quarter * 32 + lane;
             const int token0 = (tile % token_tiles) * BN;
             if (!barrier_wait(&shared->accumulator_full[slot], use & 1u, abort_flag)) { alive = false; break; }
             tensor_fence_after_sync();
             const float offset = (bias != nullptr && feature < N) ? bias[feature] : 0.0f;
             const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * BN;
-#pragma unroll 1
-            for (int chunk = 0; chunk < BN; chunk += 16) {
-                uint32_t v[16];
-                tensor_load_16(lane_base + chunk, v);
+            // Finishes one value of this thread's feature; every lane of the warp calls it together.
+            auto finish = [&](float value, int token) {
                 if (Gated) {
                     // Lanes 0-7 of each 16 hold gate rows, lanes 8-15 the matching up rows: bring them together.
-                    const int out_feature = (feature >> 4) * 8 + (feature & 7);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        // Both are rounded to the storage type first, as the unfused product would have stored them.
-                        const float mine = round_through<bf16>(__uint_as_float(v[j]) + offset);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-                        const int token = token0 + chunk + j;
-                        if ((lane & 8) == 0 && feature < N && token < M)
-                            out[static_cast<size_t>(token) * out_stride + out_feature] = from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);   // the result is rounded to bfloat16: the fast forms lose nothing
-                    }
-                } else if (feature < N) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int token = token0 + chunk + j;
-                        if (token < M) out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(__uint_as_float(v[j]) + offset);
-                    }
+                    // Both are rounded to the storage type first, as the unfused product would have stored them.
+                    const float mine = round_through<bf16>(value + offset);
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                    if ((lane & 8) == 0 && feature < N && token < M)
+                        out[static_cast<size_t>(token) * out_stride + (feature >> 4) * 8 + (feature & 7)] =
+                            from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);   // the result is rounded to bfloat16: the fast forms lose nothing
+                } else if (feature < N && token < M) {
+                    out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(value + offset);
                 }
+            };
+            if (splits == 1) {
+#pragma unroll 1
+                for (int chunk = 0; chunk < BN; chunk += 16) {
+                    uint32_t v[16];
+                    tensor_load_16(lane_base + chunk, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) finish(__uint_as_float(v[j]), token0 + chunk + j);
+                }
+                tensor_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&shared->accumulator_empty[slot]);
+                continue;
+            }
+            // A K range of the tile: the partial goes to the workspace as [token][feature of the tile].
+            const int live = min(BN, M - token0);
+            float* mine = workspace + static_cast<size_t>(item) * (BN * BM) + quarter * 32 + lane;
+#pragma unroll 1
+            for (int chunk = 0; chunk < live; chunk += 16) {
+                uint32_t v[16];
+                tensor_load_16(lane_base + chunk, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (chunk + j < live) __stcg(mine + (chunk + j) * BM, __uint_as_float(v[j]));
             }
             tensor_fence_before_sync();
             __syncwarp();
             if (lane == 0) barrier_arrive(&shared->accumulator_empty[slot]);
+            // The warp that takes the last ticket of this quarter of the tile adds the partials and stores.
+            __threadfence();
+            __syncwarp();
+            int ticket = 0;
+            if (lane == 0) ticket = atomicAdd(&tickets[tile * 4 + quarter], 1);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket != splits - 1) continue;
+            __threadfence();
+            if (lane == 0) tickets[tile * 4 + quarter] = 0;   // left at zero for the next launch
+            // Here a lane owns four neighbouring features of four tokens apart: 16-byte loads, many of them in flight,
+            // since this warp alone reads what `splits` blocks wrote.  The ranges are added in their order, whoever is last.
+            const int sub = lane >> 3, group = lane & 7;
+            const int feature4 = (tile / token_tiles) * BM + quarter * 32 + group * 4;
+            float offset4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) offset4[i] = (bias != nullptr && feature4 + i < N) ? bias[feature4 + i] : 0.0f;
+            const float4* first = reinterpret_cast<const float4*>(workspace + static_cast<size_t>(tile) * splits * (BN * BM) + quarter * 32 + group * 4);
+            constexpr int kSteps = BN / 4 < 16 ? BN / 4 : 16;
+#pragma unroll 1
+            for (int block = 0; block < live; block += 4 * kSteps) {
+                float4 sum[kSteps];
+#pragma unroll
+                for (int u = 0; u < kSteps; ++u) sum[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 1
+                for (int s = 0; s < splits; ++s) {
+                    float4 part[kSteps];
+#pragma unroll
+                    for (int u = 0; u < kSteps; ++u) {
+                        const int token = block + 4 * u + sub;
+                        part[u] = token < live ? __ldcg(first + (static_cast<size_t>(s) * BN + token) * (BM / 4)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kSteps; ++u) {
+                        sum[u].x += part[u].x; sum[u].y += part[u].y; sum[u].z += part[u].z; sum[u].w += part[u].w;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kSteps; ++u) {
+                    const int token = token0 + block + 4 * u + sub;
+                    const float value[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                    if (Gated) {
+                        // Groups 0-1 of each four hold gate rows, groups 2-3 the matching up rows (two lanes further).
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float mine = round_through<bf16>(value[i] + offset4[i]);
+                            const float other = __shfl_xor_sync(0xffffffffu, mine, 2);
+                            const int feature = feature4 + i;
+                            if ((group & 2) == 0 && feature < N && token < M)
+                                out[static_cast<size_t>(token) * out_stride + (feature >> 4) * 8 + (feature & 7)] =
+                                    from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+                        }
+                    } else if (token < M) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (feature4 + i < N) out[static_cast<size_t>(token) * out_stride + feature4 + i] = from_float<TOut>(value[i] + offset4[i]);
+                    }
+                }
+            }
         }
     }
 
@@ -317,11 +429,39 @@ int sm_count() {
     return count;
 }
 
+// Token tiles up to 128 belong to products that are bound by reading the weight (a decode batch): their blocks take
+// half an SM's shared memory, so that two are resident and the next kernel's blocks can start beside this one's.
+template <int BN> constexpr int stage_budget() { return BN <= 128 ? 100 * 1024 : 200 * 1024; }
+template <int BN> constexpr int blocks_per_sm() { return BN <= 128 ? 2 : 1; }
+
+// How many K ranges a product is cut into.  Only products of at most 128 tokens are cut: they are bound by reading the
+// weight, which wants nearly every SM reading, and pay for each further range with the last block's sum over the
+// ranges.  So: the fewest ranges that put an item on about seven SMs in eight, in one wave of resident blocks.
+// (Measured on 4096 x 4096, 6144 x 4096 and 4096 x 12288 weights at 16, 64 and 128 tokens: within 5% of the best cut.)
+int choose_splits(int M, int tiles, int k_blocks, int slots, long long workspace_floats, int tile_floats) {
+    if (M > 128 || tiles * 4 > 4096) return 1;
+    constexpr int kMinBlocks = 4;
+    const int target = sm_count() * 7 / 8;
+    int splits = (target + tiles - 1) / tiles;
+    if (splits > 8) splits = 8;
+    while (splits > 1 && (k_blocks / splits < kMinBlocks || tiles * splits > slots ||
+                          static_cast<long long>(tiles) * splits * tile_floats > workspace_floats))
+        --splits;
+    return splits;
+}
+
+struct SplitPlan {
+    int splits;              // 0: choose
+    float* workspace;
+    long long workspace_floats;
+    int* tickets;            // 4096 ints, zero between launches
+};
+
 template <int BN, typename TOut, bool Gated>
 int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const float* bias, void* out, int M, int N, int K,
-           long long out_stride, cudaStream_t stream) {
+           long long out_stride, const SplitPlan& plan, cudaStream_t stream) {
     constexpr int stage_bytes = (BM + BN) * BK * 2;
-    int stages = (200 * 1024) / stage_bytes;
+    int stages = stage_budget<BN>() / stage_bytes;
     if (stages > 8) stages = 8;
     const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
     static bool configured = false;
@@ -331,21 +471,36 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
         configured = true;
     }
     const int tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
-    const int blocks = tiles < sm_count() ? tiles : sm_count();
+    const int k_blocks = (K + BK - 1) / BK;
+    const int slots = sm_count() * blocks_per_sm<BN>();
+    int splits = 1;
+    if (plan.workspace && plan.tickets) {
+        if (plan.splits == 0) {
+            splits = choose_splits(M, tiles, k_blocks, slots, plan.workspace_floats, BN * BM);
+        } else {
+            splits = plan.splits;
+            if (splits > k_blocks || static_cast<long long>(tiles) * splits * (BN * BM) > plan.workspace_floats || tiles * 4 > 4096)
+                return cudaErrorInvalidValue;
+        }
+    } else if (plan.splits > 1) {
+        return cudaErrorInvalidValue;
+    }
+    const int items = tiles * splits;
+    const int blocks = items < slots ? items : slots;
     tau_launch(gemm_tc_kernel<BN, TOut, Gated>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
-                                                                         out_stride, stages);
+               out_stride, stages, splits, plan.workspace, plan.tickets);
     return tau_launch_status();
 }
 
 template <typename TOut, bool Gated>
 int dispatch(const CUtensorMap& weight_map, const CUtensorMap& input_map, int box, const float* bias, void* out, int M, int N, int K,
-             long long out_stride, cudaStream_t stream) {
+             long long out_stride, const SplitPlan& plan, cudaStream_t stream) {
     switch (box) {
-        case 16: return launch<16, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 32: return launch<32, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 64: return launch<64, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        case 128: return launch<128, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
-        default: return launch<256, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
+        case 16: return launch<16, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
+        case 32: return launch<32, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
+        case 64: return launch<64, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
+        case 128: return launch<128, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
+        default: return launch<256, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
     }
 }
 
@@ -360,19 +515,23 @@ TAU_EXPORT int tau_gemm_tc_status() {
 
 // bfloat16 inputs; `out_dtype` bfloat16 or float32.  Strides in elements.  `token_box` = 0 picks the token tile from M.
 // `gated`: rows of `w` are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
+// `workspace` (`workspace_floats` floats) and `tickets` (4096 ints, zero, left at zero) allow cutting along K; `splits` = 0
+// lets the launcher choose, 1 forbids it, more asks for exactly that many ranges (refused if they do not fit).
 TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
-                           long long x_stride, long long w_stride, long long out_stride, int token_box, int gated, void* stream) {
+                           long long x_stride, long long w_stride, long long out_stride, int token_box, int gated, int splits,
+                           void* workspace, long long workspace_floats, void* tickets, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out || K <= 0 || (K & 7) || (x_stride & 7) || (w_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) ||
-        (reinterpret_cast<uintptr_t>(w) & 15) || (out_dtype != TAU_BF16 && out_dtype != TAU_F32))
+        (reinterpret_cast<uintptr_t>(w) & 15) || (out_dtype != TAU_BF16 && out_dtype != TAU_F32) || splits < 0)
         return cudaErrorInvalidValue;
+    const SplitPlan plan{splits, static_cast<float*>(workspace), workspace_floats, static_cast<int*>(tickets)};
     int box = token_box;
     if (box == 0) box = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (box != 16 && box != 32 && box != 64 && box != 128 && box != 256) return cudaErrorInvalidValue;
     CUtensorMap weight_map, input_map;
     if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, box)) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (gated) return dispatch<bf16, true>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
-    if (out_dtype == TAU_BF16) return dispatch<bf16, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
-    return dispatch<float, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, s);
+    if (gated) return dispatch<bf16, true>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
+    if (out_dtype == TAU_BF16) return dispatch<bf16, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
+    return dispatch<float, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
 }

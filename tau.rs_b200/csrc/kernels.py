@@ -190,10 +190,25 @@ def _tc_fits(values, weight, out) -> bool:
             and values.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False) -> None:
+_tc_workspace = {}
+_TC_WORKSPACE_FLOATS = 2 * 148 * 128 * 128   # a 128 x 128 float partial for each of two blocks per SM: 19.4 MB
+_TC_TICKETS = 4096
+
+
+def _tc_workspace_for(device):
+    """The partial tiles and tickets of a product cut along K; one pair per device and stream order."""
+    entry = _tc_workspace.get(device)
+    if entry is None:
+        entry = _tc_workspace[device] = (torch.empty(_TC_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+                                         torch.zeros(_TC_TICKETS, dtype=torch.int32, device=device))   # zero once; the kernel leaves them at zero
+    return entry
+
+
+def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, splits: int = 0) -> None:
     """bfloat16 product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); any M and N, K % 8 == 0.
 
     `gated`: the weight's rows are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
+    `splits`: K ranges that the product is cut into (0: chosen from the sizes, for products with few tiles).
     """
     _on_device(values, weight, bias, out)
     rows, depth = values.shape
@@ -205,10 +220,12 @@ def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False) 
     _require(_tc_fits(values, weight, out), "needs K % 8 == 0 and 16-byte aligned rows")
     _f32_vector(bias, features, "the bias")
     library = build.load_library("gemm_tc.cu")
+    workspace, tickets = _tc_workspace_for(out.device)
     _check(library.tau_gemm_tc(_code(out), _pointer(values), _pointer(weight), _pointer(bias), _pointer(out), ctypes.c_int(rows),
                                ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
                                ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box),
-                               ctypes.c_int(1 if gated else 0), _stream()), "gemm_tc")
+                               ctypes.c_int(1 if gated else 0), ctypes.c_int(splits), _pointer(workspace),
+                               ctypes.c_longlong(workspace.numel()), _pointer(tickets), _stream()), "gemm_tc")
 
 
 def gemm_tc_status() -> int:

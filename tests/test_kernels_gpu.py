@@ -118,8 +118,8 @@ def test_gemm_tc(out_dtype, m, n, k, box):
     for use_bias in (None, bias):
         found = torch.full((m, n + 5), float("nan"), dtype=out_dtype, device=DEVICE)[:, :n]
         wanted = torch.empty(m, n, dtype=out_dtype)
-        kernels.gemm_tc(values, weight, use_bias, found, box)
         plain_kernels.linear(values.cpu(), weight.cpu(), None if use_bias is None else use_bias.cpu(), wanted)
+        kernels.gemm_tc(values, weight, use_bias, found, box)
         close(found, wanted, out_dtype)
     assert kernels.gemm_tc_status() == 0
 
@@ -138,6 +138,35 @@ def test_gated_products(m, n, k):
     kernels.gemm_tc(values, weight, None, found, gated=True)
     close(found, wanted, torch.bfloat16)
     assert kernels.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(40, 130, 520, 2), (64, 260, 1032, 3), (33, 128, 4096, 8), (128, 500, 584, 5), (20, 1000, 264, 4),
+                                          (200, 140, 520, 3), (64, 4096, 2048, 0), (48, 512, 4096, 0)])
+def test_gemm_tc_cut_along_k(m, n, k, splits):
+    """K ranges of a tile meet in the workspace; the last warp to arrive adds them in a fixed order.  Ragged sizes, every
+    epilogue, a second launch on the tickets that the first one left, and the same bits whoever finishes last."""
+    values = randn(m, k, dtype=torch.bfloat16, seed=23)
+    weight = randn(n, k, dtype=torch.bfloat16, seed=24)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(25)).to(DEVICE)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        wanted = torch.empty(m, n, dtype=out_dtype)
+        plain_kernels.linear(values.cpu(), weight.cpu(), bias.cpu(), wanted)
+        first = None
+        for _ in range(3):
+            found = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
+            kernels.gemm_tc(values, weight, bias, found, splits=splits)
+            close(found, wanted, out_dtype)
+            first = found if first is None else first
+            assert torch.equal(found, first)
+    if n % 16 == 0:
+        wanted = torch.empty(m, n // 2, dtype=torch.bfloat16)
+        plain_kernels.linear_gated(values.cpu(), weight.cpu(), wanted)
+        found = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEVICE)
+        kernels.gemm_tc(values, weight, None, found, gated=True, splits=splits)
+        close(found, wanted, torch.bfloat16)
+    assert kernels.gemm_tc_status() == 0
+    with pytest.raises(Exception):
+        kernels.gemm_tc(values, weight, bias, torch.empty(m, n, dtype=torch.bfloat16, device=DEVICE), splits=k // 64 + 2)   # more ranges than K blocks
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
