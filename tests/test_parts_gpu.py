@@ -1,4 +1,5 @@
-"""Each part alone against its plain function, and a toy architecture assembled from a mixer that the test defines."""
+"""Each part alone against its plain function, and toy architectures assembled from parts that the test defines:
+a mixer with state of its own, a feed-forward with routing, another position encoding."""
 import json
 import math
 
@@ -12,7 +13,8 @@ from tau_rs_b200.cache import SequenceCache
 from tau_rs_b200.config import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry, SwiGLUSpec,
                                 register_architecture, unregister_architecture)
 from tau_rs_b200.engine.batch import StepLayout, fill_step, step_views
-from tau_rs_b200.parts import CacheNeed, Mixer, build, register_mixer, unregister
+from tau_rs_b200.parts import (CacheNeed, FeedForward, Mixer, Part, build, register_feed_forward, register_mixer, register_position,
+                               unregister)
 from tau_rs_b200.weights import TensorSpec, random_tensors
 
 pytestmark = pytest.mark.gpu
@@ -270,3 +272,180 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture
         hidden = hidden + plain_model.swiglu(normed, weights, f"{prefix}.mlp", plain_model.no_rounding)
     expected = plain_model.rms_norm(hidden, weights["toy.norm.weight"], 1e-5, plain_model.no_rounding) @ weights["toy.head.weight"].t()
     assert error(alone[0], expected) < 1e-4
+
+
+# ------------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, defined here: layers of one model take different
+# feed-forwards and different position encodings, chosen by their descriptions alone.
+class RoutedSpec:
+    kind = "toy_routed"
+
+    def __init__(self, hidden, widths, top):
+        self.hidden, self.widths, self.top = hidden, tuple(widths), top       # one SwiGLU expert per width
+
+    def __eq__(self, other):
+        return isinstance(other, RoutedSpec) and (self.hidden, self.widths, self.top) == (other.hidden, other.widths, other.top)
+
+    def __hash__(self):
+        return hash((self.hidden, self.widths, self.top))
+
+
+class RoutedFeedForward(FeedForward):
+    """Router logits in 32-bit, softmax over all experts, the `top` largest renormalised, experts of unequal widths."""
+
+    def __init__(self, spec, prefix, dtype, device):
+        self.spec, self.prefix = spec, prefix
+        self.tensors = {}
+
+    def tensor_specs(self):
+        specs = {f"{self.prefix}.router.weight": TensorSpec((len(self.spec.widths), self.spec.hidden), role="vector", std=0.5)}
+        for index, width in enumerate(self.spec.widths):
+            specs[f"{self.prefix}.experts.{index}.gate_proj.weight"] = TensorSpec((width, self.spec.hidden), std=0.1)
+            specs[f"{self.prefix}.experts.{index}.up_proj.weight"] = TensorSpec((width, self.spec.hidden), std=0.1)
+            specs[f"{self.prefix}.experts.{index}.down_proj.weight"] = TensorSpec((self.spec.hidden, width), std=0.1)
+        return specs
+
+    def assign(self, name, tensor):
+        self.tensors[name] = tensor
+
+    def forward(self, hidden, step):
+        return routed_feed_forward(hidden.float(), self.tensors, self.prefix, self.spec).to(hidden.dtype)
+
+
+def routed_feed_forward(x, weights, prefix, spec):
+    scores = torch.softmax(x @ weights[f"{prefix}.router.weight"].float().t(), dim=-1)
+    best, chosen = scores.topk(spec.top, dim=-1)
+    best = best / best.sum(dim=-1, keepdim=True)
+    out = torch.zeros_like(x)
+    for index in range(len(spec.widths)):
+        gate = x @ weights[f"{prefix}.experts.{index}.gate_proj.weight"].float().t()
+        up = x @ weights[f"{prefix}.experts.{index}.up_proj.weight"].float().t()
+        expert = (torch.nn.functional.silu(gate) * up) @ weights[f"{prefix}.experts.{index}.down_proj.weight"].float().t()
+        share = (best * (chosen == index)).sum(dim=-1, keepdim=True)      # zero where the expert was not chosen
+        out += share * expert
+    return out
+
+
+class SlowedRotarySpec:
+    """Rotation angles `position / slowdown * theta^(-i / rotary_dim)`: the attention part needs only `rotary_dim` here."""
+    kind = "toy_slowed_rotary"
+
+    def __init__(self, rotary_dim, theta, slowdown, max_positions):
+        self.rotary_dim, self.theta, self.slowdown, self.max_positions = rotary_dim, theta, slowdown, max_positions
+
+    def __eq__(self, other):
+        return isinstance(other, SlowedRotarySpec) and vars(self) == vars(other)
+
+    def __hash__(self):
+        return hash(tuple(sorted(vars(self).items())))
+
+
+def slowed_tables(spec):
+    inverse = torch.tensor([spec.theta ** (-index / spec.rotary_dim) for index in range(0, spec.rotary_dim, 2)], dtype=torch.float32)
+    angles = (torch.arange(spec.max_positions, dtype=torch.float32) / spec.slowdown)[:, None] * inverse[None, :]
+    return torch.cos(angles), torch.sin(angles)
+
+
+class SlowedRotary(Part):
+    """A position encoding is a part that holds `cos` and `sin`, `[max_positions, rotary_dim / 2]` in float32, once its weights are final."""
+
+    def __init__(self, spec, device):
+        self.spec, self.device = spec, device
+        self.cos = self.sin = None
+
+    def finalize_weights(self):
+        cos, sin = slowed_tables(self.spec)
+        self.cos, self.sin = cos.contiguous().to(self.device), sin.contiguous().to(self.device)
+
+
+def routed_spec(config) -> ModelSpec:
+    hidden = config["hidden_size"]
+    norm = NormSpec(width=hidden, eps=config["eps"])
+    slowed = AttentionSpec(hidden=hidden, n_heads=3, n_kv_heads=1, head_dim=32, bias=True, softmax_scale=32 ** -0.5,
+                           qk_norm=NormSpec(width=32, eps=config["eps"]),
+                           position=SlowedRotarySpec(rotary_dim=16, theta=500.0, slowdown=config["slowdown"], max_positions=config["max_positions"]))
+    usual = AttentionSpec(hidden=hidden, n_heads=2, n_kv_heads=2, head_dim=16, bias=False, softmax_scale=0.25, qk_norm=None,
+                          position=PositionSpec(rotary_dim=16, theta=100.0, max_positions=config["max_positions"]))
+    blocks = (
+        BlockSpec("toy.layers.0", slowed, RoutedSpec(hidden, config["expert_widths"], config["experts_per_token"]), norm, norm),
+        BlockSpec("toy.layers.1", usual, SwiGLUSpec(hidden=hidden, intermediate=config["intermediate_size"]), norm, norm),
+    )
+    schedule = (ScheduleEntry(layer=0, cache_group="wide", cache_layer=0), ScheduleEntry(layer=1, cache_group="narrow", cache_layer=0))
+    return ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=config["vocab_size"], hidden=hidden, max_positions=config["max_positions"],
+                     embedding_name="toy.embed.weight", blocks=blocks, schedule=schedule, final_norm=norm,
+                     final_norm_name="toy.norm.weight", head_name="toy.head.weight", tie_head=True)
+
+
+@pytest.fixture
+def routed_architecture():
+    register_feed_forward("toy_routed")(RoutedFeedForward)
+    register_position("toy_slowed_rotary")(SlowedRotary)
+    register_architecture("ToyRoutedForCausalLM", "toy_routed", lambda raw: raw, routed_spec)
+    yield
+    unregister_architecture("ToyRoutedForCausalLM")
+    unregister("feed_forward", "toy_routed")
+    unregister("position", "toy_slowed_rotary")
+
+
+def test_a_toy_routed_feed_forward_and_another_position_encoding(routed_architecture, tmp_path):
+    config = {"architectures": ["ToyRoutedForCausalLM"], "model_type": "toy_routed", "hidden_size": 24, "intermediate_size": 40,
+              "vocab_size": 61, "max_positions": 160, "eps": 1e-5, "expert_widths": [16, 40, 8], "experts_per_token": 2, "slowdown": 4.0}
+    folder = str(tmp_path / "routed")
+    write_random_model(folder, config, seed=6, norm_jitter=0.1, storage="float32")
+    model = load_model(folder, "float32", DEVICE)
+    assert set(model.cache_groups()) == {"wide", "narrow"}
+    engine = Engine(model, 64 * 5)
+    rng = np.random.default_rng(1)
+    requests = [rng.integers(0, 61, size=length).tolist() for length in (80, 21)]
+
+    # The plain statement of the model, part by part, from the files.
+    weights = plain_model.read_plain_weights(folder)
+    spec = routed_spec(config)
+
+    def attention_run(x, prefix, attention, cos, sin):
+        count, rot = x.shape[0], attention.position.rotary_dim
+        bias = lambda name: weights[f"{prefix}.{name}.bias"] if attention.bias else 0.0
+        q = (x @ weights[f"{prefix}.q_proj.weight"].t() + bias("q_proj")).view(count, attention.n_heads, attention.head_dim)
+        k = (x @ weights[f"{prefix}.k_proj.weight"].t() + bias("k_proj")).view(count, attention.n_kv_heads, attention.head_dim)
+        v = (x @ weights[f"{prefix}.v_proj.weight"].t() + bias("v_proj")).view(count, attention.n_kv_heads, attention.head_dim)
+        if attention.qk_norm is not None:
+            q = plain_model.rms_norm(q, weights[f"{prefix}.q_norm.weight"], attention.qk_norm.eps, plain_model.no_rounding)
+            k = plain_model.rms_norm(k, weights[f"{prefix}.k_norm.weight"], attention.qk_norm.eps, plain_model.no_rounding)
+        rotate = lambda t: torch.cat([plain_model.apply_rope(t[..., :rot], cos[:count], sin[:count], plain_model.no_rounding), t[..., rot:]], dim=-1)
+        context = plain_model.causal_attention(rotate(q), rotate(k), v, plain_model.no_rounding)
+        return context.reshape(count, -1) @ weights[f"{prefix}.o_proj.weight"].t() + bias("o_proj")   # one flag for all four projections
+
+    def expected(tokens):
+        hidden = plain_model.embedding(weights["toy.embed.weight"], tokens)
+        tables = (slowed_tables(spec.blocks[0].mixer.position), plain_model.rope_tables(16, 100.0, 160))
+        for layer, block in enumerate(spec.blocks):
+            prefix = f"toy.layers.{layer}"
+            normed = plain_model.rms_norm(hidden, weights[f"{prefix}.input_layernorm.weight"], 1e-5, plain_model.no_rounding)
+            hidden = hidden + attention_run(normed, f"{prefix}.self_attn", block.mixer, *tables[layer])
+            normed = plain_model.rms_norm(hidden, weights[f"{prefix}.post_attention_layernorm.weight"], 1e-5, plain_model.no_rounding)
+            hidden = hidden + (routed_feed_forward(normed, weights, f"{prefix}.mlp", block.feed_forward) if layer == 0
+                               else plain_model.swiglu(normed, weights, f"{prefix}.mlp", plain_model.no_rounding))
+        return plain_model.rms_norm(hidden, weights["toy.norm.weight"], 1e-5, plain_model.no_rounding) @ weights["toy.embed.weight"].t()
+
+    wanted = [expected(tokens) for tokens in requests]
+    # Whole, then as a batch of unequal prompts followed by single tokens.
+    for tokens, reference in zip(requests, wanted):
+        slot = engine.open_sequence()
+        logits = engine.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu()
+        engine.close_sequence(slot)
+        assert error(logits, reference) < 1e-4
+    slots = [engine.open_sequence() for _ in requests]
+    cuts = [70, 15]
+    logits = engine.step([StepEntry(slot, tokens[:cut], [cut - 1]) for slot, tokens, cut in zip(slots, requests, cuts)]).cpu()
+    for row, cut in enumerate(cuts):
+        assert error(logits[row], wanted[row][cut - 1]) < 1e-4
+    for offset in range(6):
+        logits = engine.step([StepEntry(slots[i], [requests[i][cuts[i] + offset]], [0]) for i in range(2)]).cpu()
+        for i in range(2):
+            assert error(logits[i], wanted[i][cuts[i] + offset]) < 1e-4
+    for slot in slots:
+        engine.close_sequence(slot)
+    engine.cache.check()
+    # The slowdown is felt: the same weights with the usual tables give other logits.
+    usual = plain_model.rope_tables(16, 500.0, 160)
+    assert not torch.allclose(torch.stack(slowed_tables(spec.blocks[0].mixer.position)), torch.stack(usual))
