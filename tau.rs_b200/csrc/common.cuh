@@ -86,6 +86,27 @@ static inline int tau_launch_as(bool dependent, void (*kernel)(Parameters...), d
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, Parameters(std::forward<Arguments>(arguments))...));
 }
 
+// The same with thread-block clusters of `cluster` blocks along x (the grid's x must be a multiple of it).
+template <typename... Parameters, typename... Arguments>
+static inline int tau_launch_clusters(unsigned cluster, void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes,
+                                      cudaStream_t stream, Arguments&&... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = tau_dependent_launch_enabled() ? 2 : 1;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, Parameters(std::forward<Arguments>(arguments))...));
+}
+
 // Launches `kernel` so that it may begin before the previous kernel of the stream has finished.
 template <typename... Parameters, typename... Arguments>
 static inline int tau_launch(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,

@@ -389,6 +389,207 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     }
 }
 
+// ---- pairs of SMs on one tile ------------------------------------------------------------------------------
+// For many tokens the product is bound by the tensor cores, and a 128 x 256 tile per SM spends as much shared-memory
+// bandwidth on filling and reading its operands as the products can use.  Two blocks of a cluster therefore share a
+// 256 (features) x 256 (tokens) tile: each brings its own 128 weight rows and half of the tokens, one thread of the
+// first block issues tcgen05.mma.cta_group::2, which reads the token halves of both blocks, and each block's tensor
+// memory receives its 128 features x 256 tokens.  Per product a block now fills 32 KB of shared memory, not 48 KB.
+//
+// The first block's `full` barriers count the bytes of both blocks' copies (the peer's TMA copies signal them across
+// the cluster); tcgen05.commit signals `empty` and `accumulator_full` in both blocks; the epilogue warps of both
+// blocks release an accumulator at the first block's barrier.  All waits are bounded as above.  No copy is multicast.
+constexpr int kPairTokens = 256, kPairHalf = 128;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// The address, in the cluster's shared window, of `pointer`'s twin in the block of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_address(const void* pointer, uint32_t rank) {
+    uint32_t address;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(address) : "r"(smem_address(pointer)), "r"(rank));
+    return address;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void barrier_arrive_cluster(uint32_t cluster_barrier) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_barrier) : "memory");
+}
+
+// A TMA copy into this block's shared memory whose bytes are counted by a barrier given as a cluster address.
+__device__ __forceinline__ void tma_load_2d_pair(void* destination, const CUtensorMap* map, int inner, int outer, uint32_t cluster_barrier) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_address(destination)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(inner), "r"(outer), "r"(cluster_barrier)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mma_issue_pair(uint32_t accumulator, uint64_t a, uint64_t b, uint32_t descriptor, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(accumulator), "l"(a), "l"(b), "r"(descriptor), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives, in both blocks of the pair, at the barrier that lies where `barrier` lies, once the products issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* barrier) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_address(barrier)),
+                 "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
+
+template <typename TOut, bool Gated>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
+                    const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
+    grid_dependents_launch();
+    extern __shared__ uint8_t shared_raw[];
+    Shared* shared = reinterpret_cast<Shared*>(shared_raw);
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
+    constexpr uint32_t kWeightBytes = BM * BK * 2, kInputBytes = kPairHalf * BK * 2, kStageBytes = kWeightBytes + kInputBytes;
+    constexpr uint32_t kColumns = 2 * kPairTokens;   // two accumulators of 256 columns: all of tensor memory
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int feature_tiles = (N + 2 * BM - 1) / (2 * BM), token_tiles = (M + kPairTokens - 1) / kPairTokens;
+    const int n_tiles = feature_tiles * token_tiles;
+    const int k_blocks = (K + BK - 1) / BK;
+    volatile int* abort_flag = &shared->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            barrier_init(&shared->full[s], 1);
+            barrier_init(&shared->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            barrier_init(&shared->accumulator_full[a], 1);
+            barrier_init(&shared->accumulator_empty[a], 8);   // one arrival per epilogue warp of both blocks (used in the first block)
+        }
+        shared->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // the same warp of both blocks allocates tensor memory for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(&shared->tensor_memory_base)),
+                     "r"(kColumns)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tensor_fence_before_sync();
+    cluster_sync_all();   // both blocks' barriers exist before either signals the other's
+    tensor_fence_after_sync();
+    const uint32_t tensor_base = shared->tensor_memory_base;
+
+    if (warp == 0) {
+        // ---- producer (both blocks): this block's weight rows and its half of the tokens ----------------------
+        if (lane == 0) {
+            grid_dependency_wait();
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+                const int feature0 = (tile / token_tiles) * (2 * BM) + static_cast<int>(rank) * BM;
+                const int token0 = (tile % token_tiles) * kPairTokens + static_cast<int>(rank) * kPairHalf;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!barrier_wait(&shared->empty[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
+                    uint8_t* weight_tile = tiles + stage * kStageBytes;
+                    const uint32_t first_full = cluster_address(&shared->full[stage], 0);
+                    if (rank == 0) barrier_expect_bytes(&shared->full[stage], 2 * kStageBytes);   // the bytes of both blocks
+                    tma_load_2d_pair(weight_tile, &weight_map, kb * BK, feature0, first_full);
+                    tma_load_2d_pair(weight_tile + kWeightBytes, &input_map, kb * BK, token0, first_full);
+                    if (++stage == static_cast<uint32_t>(stages)) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: one thread of the first block, for both --------------------------------------------------
+        if (lane == 0 && rank == 0) {
+            // M = 256 over the pair, N = 256.
+            const uint32_t descriptor = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairTokens >> 3) << 17) |
+                                        (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+            uint32_t stage = 0, phase = 0, local = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
+                const uint32_t slot = local & 1u, use = local >> 1;
+                if (use > 0 && !barrier_wait(&shared->accumulator_empty[slot], (use - 1) & 1u, abort_flag)) { alive = false; break; }
+                tensor_fence_after_sync();
+                const uint32_t accumulator = tensor_base + slot * kPairTokens;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!barrier_wait(&shared->full[stage], phase, abort_flag)) { alive = false; break; }
+                    tensor_fence_after_sync();
+                    const uint32_t weight_address = smem_address(tiles + stage * kStageBytes);
+                    const uint32_t input_address = weight_address + kWeightBytes;
+#pragma unroll
+                    for (int k = 0; k < BK / kMmaK; ++k) {
+                        mma_issue_pair(accumulator, tile_descriptor(weight_address + k * kMmaK * 2), tile_descriptor(input_address + k * kMmaK * 2),
+                                       descriptor, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    mma_commit_pair(&shared->empty[stage]);   // frees the stage in both blocks
+                    if (++stage == static_cast<uint32_t>(stages)) { stage = 0; phase ^= 1u; }
+                }
+                if (alive) mma_commit_pair(&shared->accumulator_full[slot]);
+            }
+        }
+    } else {
+        // ---- epilogue (both blocks): this block's 128 features of the tile's 256 tokens ----------------------------
+        const int quarter = warp & 3;
+        uint32_t local = 0;
+        bool alive = true;
+        grid_dependency_wait();
+        for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
+            const uint32_t slot = local & 1u, use = local >> 1;
+            const int feature = (tile / token_tiles) * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32 + lane;
+            const int token0 = (tile % token_tiles) * kPairTokens;
+            if (!barrier_wait(&shared->accumulator_full[slot], use & 1u, abort_flag)) { alive = false; break; }
+            tensor_fence_after_sync();
+            const float offset = (bias != nullptr && feature < N) ? bias[feature] : 0.0f;
+            const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * kPairTokens;
+#pragma unroll 1
+            for (int chunk = 0; chunk < kPairTokens; chunk += 16) {
+                if (token0 + chunk >= M) break;   // the same for every lane
+                uint32_t v[16];
+                tensor_load_16(lane_base + chunk, v);
+                if (Gated) {
+                    const int out_feature = (feature >> 4) * 8 + (feature & 7);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float mine = round_through<bf16>(__uint_as_float(v[j]) + offset);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                        const int token = token0 + chunk + j;
+                        if ((lane & 8) == 0 && feature < N && token < M)
+                            out[static_cast<size_t>(token) * out_stride + out_feature] = from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+                    }
+                } else if (feature < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int token = token0 + chunk + j;
+                        if (token < M) out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(__uint_as_float(v[j]) + offset);
+                    }
+                }
+            }
+            tensor_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) barrier_arrive_cluster(cluster_address(&shared->accumulator_empty[slot], 0));
+        }
+    }
+
+    // ---- teardown: both blocks meet (neither's shared or tensor memory is in use by the other), then free -------------
+    tensor_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tensor_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tensor_base), "r"(kColumns) : "memory");
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -493,8 +694,29 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
 }
 
 template <typename TOut, bool Gated>
+int launch_pair(const CUtensorMap& weight_map, const CUtensorMap& input_map, const float* bias, void* out, int M, int N, int K,
+                long long out_stride, cudaStream_t stream) {
+    constexpr int stage_bytes = (BM + kPairHalf) * BK * 2;
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > 8) stages = 8;
+    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        configured = true;
+    }
+    const int tiles = ((N + 2 * BM - 1) / (2 * BM)) * ((M + kPairTokens - 1) / kPairTokens);
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    tau_launch_clusters(2, gemm_tc_pair_kernel<TOut, Gated>, dim3(2 * pairs), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias,
+                        static_cast<TOut*>(out), M, N, K, out_stride, stages);
+    return tau_launch_status();
+}
+
+template <typename TOut, bool Gated>
 int dispatch(const CUtensorMap& weight_map, const CUtensorMap& input_map, int box, const float* bias, void* out, int M, int N, int K,
              long long out_stride, const SplitPlan& plan, cudaStream_t stream) {
+    if (box == kPairHalf + 1) return launch_pair<TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, stream);
     switch (box) {
         case 16: return launch<16, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
         case 32: return launch<32, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
@@ -517,9 +739,10 @@ TAU_EXPORT int tau_gemm_tc_status() {
 // `gated`: rows of `w` are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
 // `workspace` (`workspace_floats` floats) and `tickets` (4096 ints, zero, left at zero) allow cutting along K; `splits` = 0
 // lets the launcher choose, 1 forbids it, more asks for exactly that many ranges (refused if they do not fit).
+// `pair`: 1 runs 256 x 256 tiles on pairs of SMs (only with the 256-token tile), 0 never, -1 where the 256-token tile is chosen.
 TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
                            long long x_stride, long long w_stride, long long out_stride, int token_box, int gated, int splits,
-                           void* workspace, long long workspace_floats, void* tickets, void* stream) {
+                           void* workspace, long long workspace_floats, void* tickets, int pair, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out || K <= 0 || (K & 7) || (x_stride & 7) || (w_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) ||
         (reinterpret_cast<uintptr_t>(w) & 15) || (out_dtype != TAU_BF16 && out_dtype != TAU_F32) || splits < 0)
@@ -528,8 +751,11 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     int box = token_box;
     if (box == 0) box = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (box != 16 && box != 32 && box != 64 && box != 128 && box != 256) return cudaErrorInvalidValue;
+    if (pair > 0 && (box != 256 || splits > 1)) return cudaErrorInvalidValue;
+    const bool paired = box == 256 && pair != 0 && splits <= 1;   // a cut along K that was asked for is run on single SMs
     CUtensorMap weight_map, input_map;
-    if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, box)) return cudaErrorInvalidValue;
+    if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, paired ? kPairHalf : box)) return cudaErrorInvalidValue;
+    if (paired) box = kPairHalf + 1;   // the dispatcher's mark for the paired kernel
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (gated) return dispatch<bf16, true>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);
     if (out_dtype == TAU_BF16) return dispatch<bf16, false>(weight_map, input_map, box, bias, out, M, N, K, out_stride, plan, s);

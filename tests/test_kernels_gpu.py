@@ -119,8 +119,10 @@ def test_gemm_tc(out_dtype, m, n, k, box):
         found = torch.full((m, n + 5), float("nan"), dtype=out_dtype, device=DEVICE)[:, :n]
         wanted = torch.empty(m, n, dtype=out_dtype)
         plain_kernels.linear(values.cpu(), weight.cpu(), None if use_bias is None else use_bias.cpu(), wanted)
-        kernels.gemm_tc(values, weight, use_bias, found, box)
-        close(found, wanted, out_dtype)
+        for pair in ((0, 1) if (box == 256 or (box == 0 and m > 128)) else (-1,)):   # one SM per tile, and pairs of SMs on 256 x 256 tiles
+            found.fill_(float("nan"))
+            kernels.gemm_tc(values, weight, use_bias, found, box, pair=pair)
+            close(found, wanted, out_dtype)
     assert kernels.gemm_tc_status() == 0
 
 
@@ -134,9 +136,10 @@ def test_gated_products(m, n, k):
     found = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEVICE)
     kernels.linear_gated(values, weight, found)
     close(found, wanted, torch.bfloat16)
-    found.fill_(float("nan"))
-    kernels.gemm_tc(values, weight, None, found, gated=True)
-    close(found, wanted, torch.bfloat16)
+    for pair in (0, -1):
+        found.fill_(float("nan"))
+        kernels.gemm_tc(values, weight, None, found, gated=True, pair=pair)
+        close(found, wanted, torch.bfloat16)
     assert kernels.gemm_tc_status() == 0
 
 
