@@ -635,12 +635,12 @@ int sm_count() {
 template <int BN> constexpr int stage_budget() { return BN <= 128 ? 100 * 1024 : 200 * 1024; }
 template <int BN> constexpr int blocks_per_sm() { return BN <= 128 ? 2 : 1; }
 
-// How many K ranges a product is cut into.  Only products of at most 128 tokens are cut: they are bound by reading the
-// weight, which wants nearly every SM reading, and pay for each further range with the last block's sum over the
-// ranges.  So: the fewest ranges that put an item on about seven SMs in eight, in one wave of resident blocks.
-// (Measured on 4096 x 4096, 6144 x 4096 and 4096 x 12288 weights at 16, 64 and 128 tokens: within 5% of the best cut.)
+// How many K ranges a product is cut into.  Products of few tokens are bound by reading the weight, which wants nearly
+// every SM reading; they pay for each further range with the last block's sum over the ranges.  So: the fewest ranges that
+// put an item on about seven SMs in eight, in one wave of resident blocks.  (Measured on 4096 x 4096, 6144 x 4096 and
+// 4096 x 12288 weights at 16 to 512 tokens: within 5% of the best cut.)  Beyond 1,024 tokens there are tiles enough.
 int choose_splits(int M, int tiles, int k_blocks, int slots, long long workspace_floats, int tile_floats) {
-    if (M > 128 || tiles * 4 > 4096) return 1;
+    if (M > 1024 || tiles * 4 > 4096) return 1;
     constexpr int kMinBlocks = 4;
     const int target = sm_count() * 7 / 8;
     int splits = (target + tiles - 1) / tiles;
@@ -680,7 +680,7 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
             splits = choose_splits(M, tiles, k_blocks, slots, plan.workspace_floats, BN * BM);
         } else {
             splits = plan.splits;
-            if (splits > k_blocks || static_cast<long long>(tiles) * splits * (BN * BM) > plan.workspace_floats || tiles * 4 > 4096)
+            if (splits > 1 && (splits > k_blocks || static_cast<long long>(tiles) * splits * (BN * BM) > plan.workspace_floats || tiles * 4 > 4096))
                 return cudaErrorInvalidValue;
         }
     } else if (plan.splits > 1) {
@@ -752,7 +752,11 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     if (box == 0) box = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (box != 16 && box != 32 && box != 64 && box != 128 && box != 256) return cudaErrorInvalidValue;
     if (pair > 0 && (box != 256 || splits > 1)) return cudaErrorInvalidValue;
-    const bool paired = box == 256 && pair != 0 && splits <= 1;   // a cut along K that was asked for is run on single SMs
+    bool paired = box == 256 && pair != 0 && splits <= 1;   // a cut along K is run on single SMs, whether asked for or chosen
+    if (paired && pair < 0 && splits == 0 && workspace && tickets) {
+        const int tiles = ((N + BM - 1) / BM) * ((M + 255) / 256);
+        if (choose_splits(M, tiles, (K + BK - 1) / BK, sm_count(), workspace_floats, 256 * BM) > 1) paired = false;
+    }
     CUtensorMap weight_map, input_map;
     if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, paired ? kPairHalf : box)) return cudaErrorInvalidValue;
     if (paired) box = kPairHalf + 1;   // the dispatcher's mark for the paired kernel
