@@ -2,10 +2,12 @@
 //
 // The reference runs these products through cuBLAS as m x 1 x k problems (crates/models/src/components/cuda/
 // decode/operation.rs:150-193).  Here the step is bound by reading `w` once from HBM, so the kernel is shaped
-// around that stream: a block owns 16 consecutive output features, its 16 warps split K in interleaved chunks of
-// 64 elements, cp.async keeps two chunks per warp in flight in lane-private shared-memory slots, and the few
-// activation rows are re-read from L1/L2.  (Measured on the Qwen3-8B layer shapes at 8 rows: 16 warps with two
-// chunks in flight stream 5.4 TB/s; 8 warps, deeper rings or an L2 prefetch of the block's rows are all slower.)  The arithmetic is mma.sync m16n8k16 (bfloat16 in, float accumulate) with the weight
+// around that stream: a block owns 16 consecutive output features, its warps (16, or 12 where that lets every block
+// be resident at once) split K in interleaved chunks of 64 elements, cp.async keeps two chunks per warp in flight in
+// lane-private shared-memory slots, and the few activation rows are re-read from L1/L2.  (Measured on the Qwen3-8B
+// layer shapes at 8 rows: 16 warps with two chunks in flight stream 5.4 TB/s; 8 warps, deeper rings or an L2 prefetch
+// of the block's rows are all slower; the 6144 x 4096 product, whose 384 blocks of 16 warps need a second, thin wave,
+// takes 10.0 us with 12 warps against 12.9 us.)  The arithmetic is mma.sync m16n8k16 (bfloat16 in, float accumulate) with the weight
 // rows as the A operand and the activations as B; a thread's 16-byte load is used as the fragments of two
 // consecutive MMAs, which permutes K inside a chunk identically for both operands and so leaves every dot
 // product unchanged.  Partial sums of the warps meet in shared memory.
@@ -16,16 +18,12 @@
 
 namespace {
 
-#ifndef TAU_SKINNY_WARPS
-#define TAU_SKINNY_WARPS 16
-#endif
 #ifndef TAU_SKINNY_PREFETCH
 #define TAU_SKINNY_PREFETCH 0
 #endif
 #ifndef TAU_SKINNY_MIN_BLOCKS
 #define TAU_SKINNY_MIN_BLOCKS 1
 #endif
-constexpr int kWarps = TAU_SKINNY_WARPS;
 constexpr int kRows = 16;       // output features per block
 constexpr int kChunk = 64;      // K elements per warp iteration
 
@@ -39,9 +37,11 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
 #define TAU_SKINNY_DEPTH 2
 #endif
 constexpr int kDepth = TAU_SKINNY_DEPTH;                          // chunks in flight per warp
-constexpr int kRingOnlyBytes = kWarps * kDepth * 4 * 32 * 16;     // [warp][depth][piece][lane] of 16 bytes
-constexpr int kPartialBytes = kWarps * 32 * (kRows + 1) * 4;      // the largest [warp][4 * 8 tokens][17] of floats
-constexpr int kRingBytes = kRingOnlyBytes > kPartialBytes ? kRingOnlyBytes : kPartialBytes;
+// Shared memory of a block of `warps` warps: the ring, [warp][depth][piece][lane] of 16 bytes, later reused for the
+// partial sums, at most [warp][4 * 8 tokens][17] floats.
+constexpr int ring_bytes(int warps) {
+    return warps * kDepth * 4 * 32 * 16 > warps * 32 * (kRows + 1) * 4 ? warps * kDepth * 4 * 32 * 16 : warps * 32 * (kRows + 1) * 4;
+}
 
 __device__ __forceinline__ void copy_async_16(void* destination, const void* source, bool real) {
     const unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(destination));
@@ -52,7 +52,7 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // `Gated`: a block's 16 rows are 8 gate rows followed by their 8 up rows; it writes silu(gate) * up to `out[M, N / 2]`.
-template <int NB, typename TOut, bool Gated>
+template <int NB, typename TOut, bool Gated, int kWarps>
 __global__ void __launch_bounds__(kWarps * 32, TAU_SKINNY_MIN_BLOCKS)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias, TOut* __restrict__ out,
                    int M, int N, int K, long long x_stride, long long w_stride, long long out_stride) {
@@ -158,24 +158,51 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     }
 }
 
+template <int NB, typename TOut, bool Gated, int kWarps>
+int launch_with(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride, long long w_stride,
+                long long out_stride, cudaStream_t stream, int* resident_blocks) {
+    constexpr int bytes = ring_bytes(kWarps);
+    static int resident = 0;   // blocks of this kernel that the device holds at once
+    if (!resident) {
+        cudaError_t status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, TOut, Gated, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        int device = 0, sms = 0, per_sm = 0;
+        if (status == cudaSuccess) status = cudaGetDevice(&device);
+        if (status == cudaSuccess) status = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (status == cudaSuccess)
+            status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NB, TOut, Gated, kWarps>, kWarps * 32, bytes);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        resident = per_sm * sms > 0 ? per_sm * sms : 1;
+    }
+    if (resident_blocks) {   // a query: nothing is launched
+        *resident_blocks = resident;
+        return 0;
+    }
+    const unsigned blocks = (N + kRows - 1) / kRows;
+    tau_launch(gemm_skinny_kernel<NB, TOut, Gated, kWarps>, dim3(blocks), dim3(kWarps * 32), bytes, stream, static_cast<const bf16*>(x),
+               static_cast<const bf16*>(w), bias, static_cast<TOut*>(out), M, N, K, x_stride, w_stride, out_stride);
+    return tau_launch_status();
+}
+
+// 16 warps keep the most bytes in flight; where their blocks need a second wave that 12-warp blocks (more of which are
+// resident) do not, the 12-warp form runs instead.
+template <int NB, typename TOut, bool Gated>
+int launch_typed(const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride, long long w_stride,
+                 long long out_stride, cudaStream_t stream) {
+    int wide = 0, narrow = 0;
+    int status = launch_with<NB, TOut, Gated, 16>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream, &wide);
+    if (status == 0) status = launch_with<NB, TOut, Gated, 12>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream, &narrow);
+    if (status != 0) return status;
+    const int blocks = (N + kRows - 1) / kRows;
+    if (blocks > wide && blocks <= narrow)
+        return launch_with<NB, TOut, Gated, 12>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream, nullptr);
+    return launch_with<NB, TOut, Gated, 16>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream, nullptr);
+}
+
 template <int NB, bool Gated>
 int launch(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K, long long x_stride,
            long long w_stride, long long out_stride, cudaStream_t stream) {
-    const unsigned blocks = (N + kRows - 1) / kRows;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, bf16, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-        if (status == cudaSuccess) status = cudaFuncSetAttribute(gemm_skinny_kernel<NB, float, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingBytes);
-        if (status != cudaSuccess) return static_cast<int>(status);
-        configured = true;
-    }
-    if (out_dtype == TAU_BF16)
-        tau_launch(gemm_skinny_kernel<NB, bf16, Gated>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
-                                                                        static_cast<bf16*>(out), M, N, K, x_stride, w_stride, out_stride);
-    else
-        tau_launch(gemm_skinny_kernel<NB, float, Gated>, dim3(blocks), dim3(kWarps * 32), kRingBytes, stream, static_cast<const bf16*>(x), static_cast<const bf16*>(w), bias,
-                                                                         static_cast<float*>(out), M, N, K, x_stride, w_stride, out_stride);
-    return tau_launch_status();
+    if (out_dtype == TAU_BF16) return launch_typed<NB, bf16, Gated>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream);
+    return launch_typed<NB, float, Gated>(x, w, bias, out, M, N, K, x_stride, w_stride, out_stride, stream);
 }
 
 }  // namespace
