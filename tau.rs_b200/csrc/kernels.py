@@ -155,7 +155,9 @@ def gemm_simt(values, weight, bias, out) -> None:
                                  ctypes.c_longlong(out.stride(0)), _stream()), "gemm_simt")
 
 
-SKINNY_MAX_ROWS = 32
+SKINNY_MAX_ROWS = 32      # what the skinny kernel accepts
+SKINNY_BEST_ROWS = 8      # up to here it beats the tcgen05 product cut along K (Qwen3-8B layer shapes: 72 us against 81 us per
+                          # layer at 8 rows, 97 against 82 at 12, 152 against 91 at 32)
 
 
 def _skinny_fits(values, weight, out) -> bool:
@@ -255,7 +257,7 @@ def gated_fits(in_features: int, out_features: int, dtype) -> bool:
 def linear_gated(values, weight, out) -> None:
     """`out = silu(values @ gate.T) * (values @ up.T)` in one product; `weight` holds groups of 8 gate rows followed by
     their 8 up rows (see `parts.linear.StackedLinear(interleave=...)`)."""
-    if _skinny_fits(values, weight, out):
+    if _skinny_fits(values, weight, out) and values.shape[0] <= SKINNY_BEST_ROWS:
         return gemm_skinny(values, weight, None, out, gated=True)
     _require(_tc_fits(values, weight, out), "the gated product needs bfloat16, K % 8 == 0 and 16-byte aligned rows")
     gemm_tc(values, weight, None, out, gated=True)
@@ -264,7 +266,7 @@ def linear_gated(values, weight, out) -> None:
 def linear(values, weight, bias, out) -> None:
     """`out = values @ weight.T + bias` with the kernel that fits the dtype and the sizes."""
     if values.dtype == torch.bfloat16:
-        if _skinny_fits(values, weight, out):
+        if _skinny_fits(values, weight, out) and values.shape[0] <= SKINNY_BEST_ROWS:
             return gemm_skinny(values, weight, bias, out)
         if _tc_fits(values, weight, out):
             return gemm_tc(values, weight, bias, out)
