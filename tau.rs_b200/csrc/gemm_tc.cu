@@ -662,12 +662,10 @@ template <int BN, typename TOut, bool Gated>
 int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const float* bias, void* out, int M, int N, int K,
            long long out_stride, const SplitPlan& plan, cudaStream_t stream) {
     constexpr int stage_bytes = (BM + BN) * BK * 2;
-    int stages = stage_budget<BN>() / stage_bytes;
-    if (stages > 8) stages = 8;
-    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        cudaError_t status = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(sizeof(Shared)) + 1024 + 200 * 1024);
         if (status != cudaSuccess) return static_cast<int>(status);
         configured = true;
     }
@@ -688,6 +686,12 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
     }
     const int items = tiles * splits;
     const int blocks = items < slots ? items : slots;
+    // With at most one block per SM, a block takes the whole SM's shared memory for stages: more bytes on their way
+    // (the 6144 x 4096 product at 128 tokens: 18.9 us against 23.5 us).
+    const bool roomy = blocks <= sm_count();
+    int stages = (roomy ? 200 * 1024 : stage_budget<BN>()) / stage_bytes;
+    if (stages > 8) stages = 8;
+    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
     tau_launch(gemm_tc_kernel<BN, TOut, Gated>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
                out_stride, stages, splits, plan.workspace, plan.tickets);
     return tau_launch_status();
