@@ -21,9 +21,13 @@
 // along K: a work item is (tile, K range), each item leaves its float partial tile in a workspace, and the
 // epilogue warp that arrives last at a (tile, quarter) ticket adds the partials in the order of the ranges, so
 // the sum does not depend on who finishes last, and stores the result.  No block waits for another.
+// Where all items are resident at once, the blocks of a tile are launched as one thread-block cluster instead: the
+// partials stay in shared memory, the blocks meet at the cluster's barrier, and each adds and stores a slice of
+// the tile's tokens, reading the others' partials through distributed shared memory (again in the order of the ranges).
 //
 // Needs K % 8 == 0 and 16-byte aligned rows (TMA strides); other shapes go to the plain tiled kernel.
 #include <cuda.h>
+#include <cstdio>
 
 #include "common.cuh"
 
@@ -139,6 +143,36 @@ __device__ __forceinline__ void tensor_load_16(uint32_t address, uint32_t (&v)[1
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// The address, in the cluster's shared window, of `pointer`'s twin in the block of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_address(const void* pointer, uint32_t rank) {
+    uint32_t address;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(address) : "r"(smem_address(pointer)), "r"(rank));
+    return address;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_address_of(uint32_t shared_address, int rank) {
+    uint32_t address;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(address) : "r"(shared_address), "r"(rank));
+    return address;
+}
+
+// Four floats from the shared memory of a block of the cluster (an address from `cluster_address`).
+__device__ __forceinline__ float4 cluster_load_4(uint32_t address) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(address) : "memory");
+    return v;
+}
+
 struct Shared {
     // Barriers and bookkeeping; the operand stages follow at the next 1024-byte boundary.
     uint64_t full[8];
@@ -155,13 +189,14 @@ template <int BN, typename TOut, bool Gated>
 __global__ void __launch_bounds__(kThreads, BN <= 128 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
                const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages,
-               int splits, float* __restrict__ workspace, int* __restrict__ tickets) {
+               int splits, float* __restrict__ workspace, int* __restrict__ tickets, int clustered) {
     grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
     constexpr uint32_t kWeightBytes = BM * BK * 2, kInputBytes = BN * BK * 2, kStageBytes = kWeightBytes + kInputBytes;
     constexpr uint32_t kColumns = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators; a power of two of at least 32
+    float* const own_partial = reinterpret_cast<float*>(tiles);   // clustered: [token][BM] floats over the stages, once they are done with
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feature_tiles = (N + BM - 1) / BM, token_tiles = (M + BN - 1) / BN;
@@ -305,8 +340,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
                 if (lane == 0) barrier_arrive(&shared->accumulator_empty[slot]);
                 continue;
             }
-            // A K range of the tile: the partial goes to the workspace as [token][feature of the tile].
             const int live = min(BN, M - token0);
+            if (clustered) {
+                // A K range of the tile, one of a cluster's: the partial stays here, in the memory of the stages (every
+                // product has read them: the accumulator is complete), as [token][feature of the tile].
+#pragma unroll 1
+                for (int chunk = 0; chunk < live; chunk += 16) {
+                    uint32_t v[16];
+                    tensor_load_16(lane_base + chunk, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (chunk + j < live) own_partial[(chunk + j) * BM + quarter * 32 + lane] = __uint_as_float(v[j]);
+                }
+                tensor_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) barrier_arrive(&shared->accumulator_empty[slot]);
+                continue;
+            }
+            // A K range of the tile: the partial goes to the workspace as [token][feature of the tile].
             float* mine = workspace + static_cast<size_t>(item) * (BN * BM) + quarter * 32 + lane;
 #pragma unroll 1
             for (int chunk = 0; chunk < live; chunk += 16) {
@@ -383,6 +434,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     // ---- teardown: everyone meets, then the allocating warp frees tensor memory -----------------------
     tensor_fence_before_sync();
     __syncthreads();
+    if (clustered) {
+        // The cluster's blocks hold the K ranges of one tile.  Every thread of every block comes here, also after a wait
+        // that ran out, so the two meetings below cannot be missed.  Between them each block adds, for its slice of the
+        // tile's tokens, the partials of all ranges in their order (its own among them) and stores the result.
+        cluster_sync_all();
+        if (*abort_flag == 0) {
+            grid_dependency_wait();
+            const int tile = blockIdx.x / splits;
+            const int rank = static_cast<int>(cluster_rank());
+            const int feature0 = (tile / token_tiles) * BM, token0 = (tile % token_tiles) * BN;
+            const int live = min(BN, M - token0);
+            const int per = (live + splits - 1) / splits;
+            const int first = rank * per, count = max(0, min(per, live - first));
+            const int group = threadIdx.x & 31;                 // four neighbouring features of the tile; a warp spans its 128
+            const int feature4 = feature0 + group * 4;
+            float offset4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) offset4[i] = (bias != nullptr && feature4 + i < N) ? bias[feature4 + i] : 0.0f;
+            const uint32_t own = smem_address(own_partial);
+            for (int row = warp; row < count; row += kThreads / 32) {
+                const int token_in_tile = first + row;
+                const uint32_t address = own + static_cast<uint32_t>((token_in_tile * BM + group * 4) * 4);
+                float4 part[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r)   // all ranges' loads leave together
+                    part[r] = r < splits ? cluster_load_4(cluster_address_of(address, r)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                float value[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    if (r < splits) { value[0] += part[r].x; value[1] += part[r].y; value[2] += part[r].z; value[3] += part[r].w; }
+                const int token = token0 + token_in_tile;
+                if (Gated) {
+                    // Groups 0-1 of each four hold gate rows, groups 2-3 the matching up rows (two lanes further).
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float mine = round_through<bf16>(value[i] + offset4[i]);
+                        const float other = __shfl_xor_sync(0xffffffffu, mine, 2);
+                        const int feature = feature4 + i;
+                        if ((group & 2) == 0 && feature < N)
+                            out[static_cast<size_t>(token) * out_stride + (feature >> 4) * 8 + (feature & 7)] =
+                                from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (feature4 + i < N) out[static_cast<size_t>(token) * out_stride + feature4 + i] = from_float<TOut>(value[i] + offset4[i]);
+                }
+            }
+        }
+        cluster_sync_all();   // nobody leaves while another still reads its partial
+    }
     if (warp == 1) {
         tensor_fence_after_sync();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tensor_base), "r"(kColumns) : "memory");
@@ -400,23 +502,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
 // the cluster); tcgen05.commit signals `empty` and `accumulator_full` in both blocks; the epilogue warps of both
 // blocks release an accumulator at the first block's barrier.  All waits are bounded as above.  No copy is multicast.
 constexpr int kPairTokens = 256, kPairHalf = 128;
-
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t rank;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-    return rank;
-}
-
-// The address, in the cluster's shared window, of `pointer`'s twin in the block of rank `rank`.
-__device__ __forceinline__ uint32_t cluster_address(const void* pointer, uint32_t rank) {
-    uint32_t address;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(address) : "r"(smem_address(pointer)), "r"(rank));
-    return address;
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 
 __device__ __forceinline__ void barrier_arrive_cluster(uint32_t cluster_barrier) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_barrier) : "memory");
@@ -656,6 +741,7 @@ struct SplitPlan {
     float* workspace;
     long long workspace_floats;
     int* tickets;            // 4096 ints, zero between launches
+    int cluster;             // 0: the ranges of a tile meet in the workspace even where a cluster could be formed
 };
 
 template <int BN, typename TOut, bool Gated>
@@ -688,12 +774,57 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
     const int blocks = items < slots ? items : slots;
     // With at most one block per SM, a block takes the whole SM's shared memory for stages: more bytes on their way
     // (the 6144 x 4096 product at 128 tokens: 18.9 us against 23.5 us).
-    const bool roomy = blocks <= sm_count();
-    int stages = (roomy ? 200 * 1024 : stage_budget<BN>()) / stage_bytes;
-    if (stages > 8) stages = 8;
-    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
+    bool roomy = blocks <= sm_count();
+    auto shared_for = [&](bool whole_sm, int* stage_count) {
+        int count = (whole_sm ? 200 * 1024 : stage_budget<BN>()) / stage_bytes;
+        if (count > 8) count = 8;
+        *stage_count = count;
+        return static_cast<int>(sizeof(Shared)) + 1024 + count * stage_bytes;
+    };
+    int stages = 0;
+    int shared_bytes = shared_for(roomy, &stages);
+    // All items resident at once: the ranges of a tile form a cluster and meet in shared memory.  A cluster is placed
+    // inside one GPC, so fewer clusters fit than blocks alone would: 48 clusters of 3 whole-SM blocks did not fit the
+    // 148 SMs and took two waves.  For whole-SM blocks the driver says how many clusters fit; half-SM blocks (for which
+    // its answer was the same, though twice as many ran at once) are clustered while they fill at most three quarters
+    // of their places.
+    if (splits > 1 && splits <= 8 && items == blocks && plan.cluster != 0) {
+        bool whole = false;
+        if (roomy || blocks_per_sm<BN>() == 1) {
+            static int fits[9] = {};   // clusters of whole-SM blocks of this size that are resident at once: 0 unknown, -1 no answer
+            int& known = fits[splits];
+            if (known == 0) {
+                int whole_stages = 0;
+                cudaLaunchConfig_t config = {};
+                config.gridDim = dim3(blocks);
+                config.blockDim = dim3(kThreads);
+                config.dynamicSmemBytes = shared_for(true, &whole_stages);
+                cudaLaunchAttribute attribute[1];
+                attribute[0].id = cudaLaunchAttributeClusterDimension;
+                attribute[0].val.clusterDim.x = splits;
+                attribute[0].val.clusterDim.y = 1;
+                attribute[0].val.clusterDim.z = 1;
+                config.attrs = attribute;
+                config.numAttrs = 1;
+                int clusters = 0;
+                known = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_kernel<BN, TOut, Gated>, &config) == cudaSuccess && clusters > 0 ? clusters : -1;
+                if (known < 0) cudaGetLastError();
+            }
+            whole = known >= tiles;
+        }
+        const bool half = !whole && blocks_per_sm<BN>() == 2 && items <= sm_count() * 2 * 3 / 4;
+        if (whole || half) {
+            int cluster_stages = 0;
+            const int cluster_bytes = shared_for(whole, &cluster_stages);
+            if (cluster_stages * stage_bytes >= BN * BM * 4) {   // the partial tile lies over the stages
+                tau_launch_clusters(splits, gemm_tc_kernel<BN, TOut, Gated>, dim3(blocks), dim3(kThreads), cluster_bytes, stream, weight_map, input_map,
+                                    bias, static_cast<TOut*>(out), M, N, K, out_stride, cluster_stages, splits, plan.workspace, plan.tickets, 1);
+                return tau_launch_status();
+            }
+        }
+    }
     tau_launch(gemm_tc_kernel<BN, TOut, Gated>, dim3(blocks), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias, static_cast<TOut*>(out), M, N, K,
-               out_stride, stages, splits, plan.workspace, plan.tickets);
+               out_stride, stages, splits, plan.workspace, plan.tickets, 0);
     return tau_launch_status();
 }
 
@@ -743,15 +874,16 @@ TAU_EXPORT int tau_gemm_tc_status() {
 // `gated`: rows of `w` are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
 // `workspace` (`workspace_floats` floats) and `tickets` (4096 ints, zero, left at zero) allow cutting along K; `splits` = 0
 // lets the launcher choose, 1 forbids it, more asks for exactly that many ranges (refused if they do not fit).
+// `cluster`: 0 keeps the ranges of a tile from meeting in a cluster's shared memory (they meet in the workspace).
 // `pair`: 1 runs 256 x 256 tiles on pairs of SMs (only with the 256-token tile), 0 never, -1 where the 256-token tile is chosen.
 TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const float* bias, void* out, int M, int N, int K,
                            long long x_stride, long long w_stride, long long out_stride, int token_box, int gated, int splits,
-                           void* workspace, long long workspace_floats, void* tickets, int pair, void* stream) {
+                           void* workspace, long long workspace_floats, void* tickets, int pair, int cluster, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!x || !w || !out || K <= 0 || (K & 7) || (x_stride & 7) || (w_stride & 7) || (reinterpret_cast<uintptr_t>(x) & 15) ||
         (reinterpret_cast<uintptr_t>(w) & 15) || (out_dtype != TAU_BF16 && out_dtype != TAU_F32) || splits < 0)
         return cudaErrorInvalidValue;
-    const SplitPlan plan{splits, static_cast<float*>(workspace), workspace_floats, static_cast<int*>(tickets)};
+    const SplitPlan plan{splits, static_cast<float*>(workspace), workspace_floats, static_cast<int*>(tickets), cluster};
     int box = token_box;
     if (box == 0) box = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     if (box != 16 && box != 32 && box != 64 && box != 128 && box != 256) return cudaErrorInvalidValue;

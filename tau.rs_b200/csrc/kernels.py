@@ -206,11 +206,13 @@ def _tc_workspace_for(device):
     return entry
 
 
-def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, splits: int = 0, pair: int = -1) -> None:
+def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, splits: int = 0, pair: int = -1, cluster: bool = True) -> None:
     """bfloat16 product on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); any M and N, K % 8 == 0.
 
     `gated`: the weight's rows are groups of 8 gate rows and their 8 up rows; `out` is `[M, N / 2]` = silu(gate) * up.
     `splits`: K ranges that the product is cut into (0: chosen from the sizes, for products with few tiles).
+    `cluster`: False makes the K ranges of a tile meet in a workspace in global memory even where they could meet in the
+    shared memory of a thread-block cluster.
     `pair`: 256 x 256 tiles on pairs of SMs (tcgen05 `cta_group::2`) where the 256-token tile is used: -1 yes, 0 no, 1 insist.
     """
     _on_device(values, weight, bias, out)
@@ -228,7 +230,7 @@ def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, 
                                ctypes.c_int(features), ctypes.c_int(depth), ctypes.c_longlong(values.stride(0)),
                                ctypes.c_longlong(weight.stride(0)), ctypes.c_longlong(out.stride(0)), ctypes.c_int(token_box),
                                ctypes.c_int(1 if gated else 0), ctypes.c_int(splits), _pointer(workspace),
-                               ctypes.c_longlong(workspace.numel()), _pointer(tickets), ctypes.c_int(pair), _stream()), "gemm_tc")
+                               ctypes.c_longlong(workspace.numel()), _pointer(tickets), ctypes.c_int(pair), ctypes.c_int(1 if cluster else 0), _stream()), "gemm_tc")
 
 
 def gemm_tc_status() -> int:

@@ -155,9 +155,9 @@ def test_gemm_tc_cut_along_k(m, n, k, splits):
         wanted = torch.empty(m, n, dtype=out_dtype)
         plain_kernels.linear(values.cpu(), weight.cpu(), bias.cpu(), wanted)
         first = None
-        for _ in range(3):
+        for attempt in range(4):   # the ranges meet in a cluster's shared memory, or in the workspace: the same sums in the same order
             found = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEVICE)
-            kernels.gemm_tc(values, weight, bias, found, splits=splits)
+            kernels.gemm_tc(values, weight, bias, found, splits=splits, cluster=attempt % 2 == 0)
             close(found, wanted, out_dtype)
             first = found if first is None else first
             assert torch.equal(found, first)
@@ -165,8 +165,10 @@ def test_gemm_tc_cut_along_k(m, n, k, splits):
         wanted = torch.empty(m, n // 2, dtype=torch.bfloat16)
         plain_kernels.linear_gated(values.cpu(), weight.cpu(), wanted)
         found = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEVICE)
-        kernels.gemm_tc(values, weight, None, found, gated=True, splits=splits)
-        close(found, wanted, torch.bfloat16)
+        for cluster in (True, False):
+            found.fill_(float("nan"))
+            kernels.gemm_tc(values, weight, None, found, gated=True, splits=splits, cluster=cluster)
+            close(found, wanted, torch.bfloat16)
     assert kernels.gemm_tc_status() == 0
     with pytest.raises(Exception):
         kernels.gemm_tc(values, weight, bias, torch.empty(m, n, dtype=torch.bfloat16, device=DEVICE), splits=k // 64 + 2)   # more ranges than K blocks
