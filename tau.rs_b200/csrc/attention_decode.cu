@@ -39,7 +39,7 @@ __device__ __forceinline__ float exponential(float value) { return expf(value); 
 constexpr int PER = (D + 31) / 32;            // value columns per lane
 constexpr bool kContiguous = (D % 32 == 0);   // lane owns PER neighbouring columns, else columns lane, lane + 32, ...
 
-__device__ __forceinline__ void load_vec(const T* source, float (&out)[kVec]) {
+[[maybe_unused]] __device__ __forceinline__ void load_vec(const T* source, float (&out)[kVec]) {
     const uint4 raw = *reinterpret_cast<const uint4*>(source);
 #if TAU_DTYPE == 1
     const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -56,7 +56,7 @@ __device__ __forceinline__ void load_vec(const T* source, float (&out)[kVec]) {
 
 __device__ __forceinline__ int column_of(int lane, int i) { return kContiguous ? lane * PER + i : lane + 32 * i; }
 
-__device__ __forceinline__ void load_columns(const T* row, int lane, float (&out)[PER]) {
+[[maybe_unused]] __device__ __forceinline__ void load_columns(const T* row, int lane, float (&out)[PER]) {
     if constexpr (kContiguous && PER * sizeof(T) == 16) {
         const uint4 raw = *reinterpret_cast<const uint4*>(row + lane * PER);
         const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -566,7 +566,7 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
 }
 #endif  // TAU_DTYPE == 1
 
-__global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+[[maybe_unused]] __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       T* __restrict__ out, int n_heads, int splits) {
     grid_dependents_launch();
     grid_dependency_wait();

@@ -37,14 +37,13 @@ constexpr int kHalves = D / 64;         // 64-element (128-byte) slices of the h
 constexpr int kThreads = 192;
 constexpr int kQBytes = BM * D * 2;
 constexpr int kKeyBytes = BN * D * 2;   // a key tile, or a value tile
-constexpr int kProbabilityBytes = BM * BN * 2;
-constexpr int kKeyAreaBytes = kKeyBytes > kProbabilityBytes ? kKeyBytes : kProbabilityBytes;   // the probabilities of a tile take the key tile's place
-constexpr int kStageBytes = kKeyAreaBytes + kKeyBytes;
+constexpr int kStageBytes = 2 * kKeyBytes;   // a key tile and a value tile; the rings of the two are handed over separately
 #ifndef TAU_ATTN_STAGES
 #define TAU_ATTN_STAGES 2
 #endif
 constexpr int kStages = TAU_ATTN_STAGES;          // 2: two blocks per SM (62 us for 2,048 tokens of 32 heads); 3: one block per SM (73 us)
-constexpr uint32_t kColumns = 256;      // two score buffers in columns [0, 64) and [64, 128), O in columns [128, 128 + D)
+constexpr uint32_t kColumns = 256;      // two score buffers in columns [0, 64) and [64, 128), O in columns [128, 128 + D);
+                                        // the probabilities of a tile (bfloat16 pairs, 32 columns) take the place of its scores
 constexpr uint32_t kOColumn = 128;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
@@ -126,6 +125,15 @@ __device__ __forceinline__ void mma_issue(uint32_t accumulator, uint64_t a, uint
         ::"r"(accumulator), "l"(a), "l"(b), "r"(descriptor), "r"(accumulate)
         : "memory");
 }
+// The same with the A operand in tensor memory (lane = row, a column holds two neighbouring bfloat16 of K).
+__device__ __forceinline__ void mma_issue_from_tensor(uint32_t accumulator, uint32_t a, uint64_t b, uint32_t descriptor, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(accumulator), "r"(a), "l"(b), "r"(descriptor), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint64_t* barrier) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(barrier)) : "memory");
 }
@@ -164,6 +172,17 @@ __device__ __forceinline__ void tensor_store_32(uint32_t address, const float (&
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tensor_store_words_32(uint32_t address, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+          "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+          "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // 2^x on the special-function unit, one instruction (inputs here are <= 8 or -inf; tiny results may flush to zero).
 __device__ __forceinline__ float fast_exp2(float value) {
     float result;
@@ -178,11 +197,13 @@ __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
 
 struct Shared {
     uint64_t q_full;
-    uint64_t kv_full[kStages];      // a key and value tile has landed
-    uint64_t stage_free[kStages];   // the second product that read a stage has finished
+    uint64_t k_full[kStages];       // a key tile has landed
+    uint64_t v_full[kStages];       // a value tile has landed
+    uint64_t k_free[kStages];       // the first product that read a key tile has finished
+    uint64_t v_free[kStages];       // the second product that read a value tile has finished
     uint64_t s_full[2];             // scores of a tile are in their buffer of tensor memory
     uint64_t s_free[2];             // the softmax has read that buffer
-    uint64_t p_ready[2];            // probabilities of a tile are in shared memory (and O has been rescaled if need be)
+    uint64_t p_ready[2];            // probabilities of a tile are in tensor memory (and O has been rescaled if need be)
     uint64_t pv_done;               // the second product of a tile has finished
     uint32_t tensor_memory_base;
     int abort_flag;
@@ -198,15 +219,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
     uint8_t* q_tile = tiles;                      // kHalves slices of [128 rows x 128 bytes]
-    uint8_t* stages = tiles + kQBytes;            // per stage: key tile (later the probabilities), value tile
+    uint8_t* key_tiles = tiles + kQBytes;                          // kStages key tiles
+    uint8_t* value_tiles = key_tiles + kStages * kKeyBytes;        // kStages value tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &shared->abort_flag;
 
     if (threadIdx.x == 0) {
         barrier_init(&shared->q_full, 1);
         for (int s = 0; s < kStages; ++s) {
-            barrier_init(&shared->kv_full[s], 1);
-            barrier_init(&shared->stage_free[s], 1);
+            barrier_init(&shared->k_full[s], 1);
+            barrier_init(&shared->v_full[s], 1);
+            barrier_init(&shared->k_free[s], 1);
+            barrier_init(&shared->v_free[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             barrier_init(&shared->s_full[b], 1);
@@ -259,18 +283,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             barrier_expect_bytes(&shared->q_full, kQBytes);
             for (int half = 0; half < kHalves; ++half)
                 tma_load_2d(q_tile + half * (BM * 128), &q_map, head * D + half * 64, row0 + block * BM, &shared->q_full);
-            for (int i = 0; i < n_tiles; ++i) {
+            // Key tile i is free again when the scores of tile i - kStages are done, which is earlier than the value tile of
+            // the same stage (free when the second product of tile i - kStages is done): keys are asked for one tile ahead
+            // of values, in the order in which their places come free.
+            auto load_keys = [&](int i) {
                 const int s = i % kStages;
                 const uint32_t use = i / kStages;
-                if (use > 0 && !barrier_wait(&shared->stage_free[s], (use - 1) & 1u, abort_flag)) break;
-                uint8_t* key_tile = stages + s * kStageBytes;
+                if (use > 0 && !barrier_wait(&shared->k_free[s], (use - 1) & 1u, abort_flag)) return false;
                 const int row = (pages[first_tile + i] * n_kv_heads + kv_head) * BN;
-                barrier_expect_bytes(&shared->kv_full[s], 2 * kKeyBytes);
-                for (int half = 0; half < kHalves; ++half) {
-                    tma_load_2d(key_tile + half * (BN * 128), &k_map, half * 64, row, &shared->kv_full[s]);
-                    tma_load_2d(key_tile + kKeyAreaBytes + half * (BN * 128), &v_map, half * 64, row, &shared->kv_full[s]);
-                }
+                barrier_expect_bytes(&shared->k_full[s], kKeyBytes);
+                for (int half = 0; half < kHalves; ++half)
+                    tma_load_2d(key_tiles + s * kKeyBytes + half * (BN * 128), &k_map, half * 64, row, &shared->k_full[s]);
+                return true;
+            };
+            auto load_values = [&](int i) {
+                const int s = i % kStages;
+                const uint32_t use = i / kStages;
+                if (use > 0 && !barrier_wait(&shared->v_free[s], (use - 1) & 1u, abort_flag)) return false;
+                const int row = (pages[first_tile + i] * n_kv_heads + kv_head) * BN;
+                barrier_expect_bytes(&shared->v_full[s], kKeyBytes);
+                for (int half = 0; half < kHalves; ++half)
+                    tma_load_2d(value_tiles + s * kKeyBytes + half * (BN * 128), &v_map, half * 64, row, &shared->v_full[s]);
+                return true;
+            };
+            bool alive = true;
+            for (int i = 0; i < n_tiles && alive; ++i) {
+                alive = load_keys(i);
+                if (alive && i > 0) alive = load_values(i - 1);
             }
+            if (alive && n_tiles > 0) load_values(n_tiles - 1);
         }
     } else if (warp == 5) {
         // ---- MMA issuer -----------------------------------------------------------------------------------------
@@ -281,8 +322,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // fill the other score buffer, and the second product of tile i follows as soon as its probabilities are there.
             auto issue_scores = [&](int i) {
                 const int s = i % kStages;
-                const uint32_t key_address = smem_address(stages + s * kStageBytes);
-                if (!barrier_wait(&shared->kv_full[s], (i / kStages) & 1u, abort_flag)) return false;
+                const uint32_t key_address = smem_address(key_tiles + s * kKeyBytes);
+                if (!barrier_wait(&shared->k_full[s], (i / kStages) & 1u, abort_flag)) return false;
+                // The buffer also held the probabilities of tile i - 2; their product was issued before this one and the
+                // tensor core takes products in the order of issue, so only the softmax's read needs waiting for.
                 if (i >= 2 && !barrier_wait(&shared->s_free[i & 1], ((i >> 1) - 1) & 1u, abort_flag)) return false;
                 tensor_fence_after_sync();
 #pragma unroll
@@ -292,6 +335,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     mma_issue(tensor_base + (i & 1) * BN, k_major_descriptor(q_address + offset),
                               k_major_descriptor(key_address + key_offset), score_descriptor, k > 0 ? 1u : 0u);
                 }
+                mma_commit(&shared->k_free[s]);
                 mma_commit(&shared->s_full[i & 1]);
                 return true;
             };
@@ -299,16 +343,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             for (int i = 0; i < n_tiles && alive; ++i) {
                 if (i + 1 < n_tiles && !issue_scores(i + 1)) break;
                 const int s = i % kStages;
-                const uint32_t key_address = smem_address(stages + s * kStageBytes), value_address = key_address + kKeyAreaBytes;
-                // Probabilities lie where the key tile was.
+                const uint32_t value_address = smem_address(value_tiles + s * kKeyBytes);
+                if (!barrier_wait(&shared->v_full[s], (i / kStages) & 1u, abort_flag)) break;
+                // Probabilities lie where the scores of the tile were: 16 keys are 8 columns.
                 if (!barrier_wait(&shared->p_ready[i & 1], (i >> 1) & 1u, abort_flag)) break;
                 tensor_fence_after_sync();
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
-                    mma_issue(tensor_base + kOColumn, k_major_descriptor(key_address + k * 32), mn_major_descriptor(value_address + k * 2048),
-                              value_descriptor, (i > 0 || k > 0) ? 1u : 0u);
+                    mma_issue_from_tensor(tensor_base + kOColumn, tensor_base + (i & 1) * BN + k * 8, mn_major_descriptor(value_address + k * 2048),
+                                          value_descriptor, (i > 0 || k > 0) ? 1u : 0u);
                 }
-                mma_commit(&shared->stage_free[s]);
+                mma_commit(&shared->v_free[s]);
                 mma_commit(&shared->pv_done);
             }
         }
@@ -343,8 +388,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             if (key0 + BN - 1 > last_position) {
                 // Rows of the page beyond the last position hold whatever an earlier sequence left there.  Their
                 // probabilities are zero, but zero times a stale NaN is not: clear those value rows before the product.
-                uint8_t* value_tile = stages + s * kStageBytes + kKeyAreaBytes;
+                uint8_t* value_tile = value_tiles + s * kKeyBytes;
                 const int first_stale = last_position - key0 + 1;
+                if (!barrier_wait(&shared->v_full[s], (i / kStages) & 1u, abort_flag)) { alive = false; break; }   // the tile must have landed first
                 for (int item = threadIdx.x; item < (BN - first_stale) * kHalves * 8; item += 128) {
                     const int chunk = item % 8, half = (item / 8) % kHalves, stale_row = first_stale + item / (8 * kHalves);
                     *reinterpret_cast<uint4*>(value_tile + half * (BN * 128) + stale_row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -388,22 +434,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 shift = tile_max;
             }
             const float subtract = shift == -INFINITY ? 0.0f : shift;   // a row that has seen no key yet
-            // Probabilities: row `row` of a [128 x 64] K-major tile, 16-byte chunk c at (c ^ (row % 8)).
-            uint8_t* p_row = stages + s * kStageBytes + row * 128;
+            // Probabilities: this row's 64 values as 32 pairs of bfloat16, written over the row's scores in tensor memory,
+            // where the second product takes them as its A operand.
+            uint32_t packed[BN / 2];
             float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int c = 0; c < BN / 8; ++c) {
-                float p[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    p[j] = fast_exp2(fmaf(score[c * 8 + j], scale_log2, -subtract));
-                    partial_sum[j & 3] += p[j];
-                }
-                const uint4 packed = make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = packed;
+            for (int j = 0; j < BN; j += 2) {
+                const float p0 = fast_exp2(fmaf(score[j], scale_log2, -subtract));
+                const float p1 = fast_exp2(fmaf(score[j + 1], scale_log2, -subtract));
+                partial_sum[j & 3] += p0;
+                partial_sum[(j + 1) & 3] += p1;
+                packed[j / 2] = pack_bf16(p0, p1);
             }
             sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads shared memory through the async proxy
+            tensor_store_words_32(lane_base + (i & 1) * BN, packed);
+            if (key0 + BN - 1 > last_position) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared value rows, for the tensor core's reads
             tensor_fence_before_sync();
             __syncwarp();
             if (lane == 0) barrier_arrive(&shared->p_ready[i & 1]);

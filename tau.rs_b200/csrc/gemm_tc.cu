@@ -38,13 +38,6 @@ constexpr int BK = 64;         // K elements per stage: 128 bytes, one swizzle r
 constexpr int kMmaK = 16;      // K of one tcgen05.mma for 16-bit inputs
 constexpr int kThreads = 192;        // producer, issuer, four epilogue warps
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-#ifndef TAU_TC_ROTATE
-#define TAU_TC_ROTATE 0
-#endif
-
-// Where in its K range an item starts (it wraps around): items that run side by side then read different columns
-// of the weight at any moment instead of all the same one.
-__device__ __forceinline__ int first_block(int item, int count) { return TAU_TC_ROTATE ? (item * TAU_TC_ROTATE) % count : 0; }
 
 __device__ int gemm_tc_error = 0;   // raised when a wait ran out; read by tau_gemm_tc_status
 
@@ -248,9 +241,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
                 const int tile = item / splits, split = item - tile * splits;
                 const int feature0 = (tile / token_tiles) * BM, token0 = (tile % token_tiles) * BN;
                 const int kb_begin = k_blocks * split / splits, count = k_blocks * (split + 1) / splits - kb_begin;
-                const int shift = first_block(item, count);
                 for (int i = 0; i < count; ++i) {
-                    const int kb = kb_begin + (i + shift < count ? i + shift : i + shift - count);
+                    const int kb = kb_begin + i;
                     if (!waited && held == stages) release();
                     if (!barrier_wait(&shared->empty[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
                     uint8_t* weight_tile = tiles + stage * kStageBytes;
