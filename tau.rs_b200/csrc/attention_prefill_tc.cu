@@ -37,11 +37,16 @@ constexpr int kHalves = D / 64;         // 64-element (128-byte) slices of the h
 constexpr int kThreads = 192;
 constexpr int kQBytes = BM * D * 2;
 constexpr int kKeyBytes = BN * D * 2;   // a key tile, or a value tile
-constexpr int kStageBytes = 2 * kKeyBytes;   // a key tile and a value tile; the rings of the two are handed over separately
-#ifndef TAU_ATTN_STAGES
-#define TAU_ATTN_STAGES 2
+#ifndef TAU_ATTN_KEY_STAGES
+#define TAU_ATTN_KEY_STAGES 2
 #endif
-constexpr int kStages = TAU_ATTN_STAGES;          // 2: two blocks per SM (62 us for 2,048 tokens of 32 heads); 3: one block per SM (73 us)
+constexpr int kKeyStages = TAU_ATTN_KEY_STAGES;   // key tiles in flight: a key tile is free as soon as its scores are done
+constexpr int kValueStages = 2;                   // value tiles in flight: free when the second product of their tile is done
+// Shared memory: Q, the key ring, the value ring, then the barriers; nothing is spent on aligning the tiles (dynamic
+// shared memory starts at a multiple of 1,024 bytes, which the kernel checks before it does anything else), so that
+// even three key stages at head size 128 (112 KB + 136 bytes) leave room for two blocks per SM.  A third key stage
+// changed nothing (47.5 us against 47.4 us at 2,048 tokens, 514 against 509 us at 8,192): the keys are not what the
+// tensor core waits for.
 constexpr uint32_t kColumns = 256;      // two score buffers in columns [0, 64) and [64, 128), O in columns [128, 128 + D);
                                         // the probabilities of a tile (bfloat16 pairs, 32 columns) take the place of its scores
 constexpr uint32_t kOColumn = 128;
@@ -197,10 +202,10 @@ __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
 
 struct Shared {
     uint64_t q_full;
-    uint64_t k_full[kStages];       // a key tile has landed
-    uint64_t v_full[kStages];       // a value tile has landed
-    uint64_t k_free[kStages];       // the first product that read a key tile has finished
-    uint64_t v_free[kStages];       // the second product that read a value tile has finished
+    uint64_t k_full[kKeyStages];    // a key tile has landed
+    uint64_t v_full[kValueStages];  // a value tile has landed
+    uint64_t k_free[kKeyStages];    // the first product that read a key tile has finished
+    uint64_t v_free[kValueStages];  // the second product that read a value tile has finished
     uint64_t s_full[2];             // scores of a tile are in their buffer of tensor memory
     uint64_t s_free[2];             // the softmax has read that buffer
     uint64_t p_ready[2];            // probabilities of a tile are in tensor memory (and O has been rescaled if need be)
@@ -209,27 +214,33 @@ struct Shared {
     int abort_flag;
 };
 
-__global__ void __launch_bounds__(kThreads, kStages == 2 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_start, const int* __restrict__ page_rows, int page_stride, int n_seqs,
                             int n_heads, int n_kv_heads, float scale, int window) {
     grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
-    Shared* shared = reinterpret_cast<Shared*>(shared_raw);
-    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_tile = tiles;                      // kHalves slices of [128 rows x 128 bytes]
-    uint8_t* key_tiles = tiles + kQBytes;                          // kStages key tiles
-    uint8_t* value_tiles = key_tiles + kStages * kKeyBytes;        // kStages value tiles
+    uint8_t* tiles = shared_raw;                                   // the swizzled tiles need 1,024-byte alignment
+    uint8_t* q_tile = tiles;                                       // kHalves slices of [128 rows x 128 bytes]
+    uint8_t* key_tiles = tiles + kQBytes;                          // kKeyStages key tiles
+    uint8_t* value_tiles = key_tiles + kKeyStages * kKeyBytes;     // kValueStages value tiles
+    Shared* shared = reinterpret_cast<Shared*>(value_tiles + kValueStages * kKeyBytes);
+    if ((smem_address(shared_raw) & 1023u) != 0u) {   // never seen; the same for every thread, before anything is set up
+        if (threadIdx.x == 0) atomicExch(&attention_tc_error, 2);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &shared->abort_flag;
 
     if (threadIdx.x == 0) {
         barrier_init(&shared->q_full, 1);
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kKeyStages; ++s) {
             barrier_init(&shared->k_full[s], 1);
-            barrier_init(&shared->v_full[s], 1);
             barrier_init(&shared->k_free[s], 1);
+        }
+        for (int s = 0; s < kValueStages; ++s) {
+            barrier_init(&shared->v_full[s], 1);
             barrier_init(&shared->v_free[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -283,12 +294,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             barrier_expect_bytes(&shared->q_full, kQBytes);
             for (int half = 0; half < kHalves; ++half)
                 tma_load_2d(q_tile + half * (BM * 128), &q_map, head * D + half * 64, row0 + block * BM, &shared->q_full);
-            // Key tile i is free again when the scores of tile i - kStages are done, which is earlier than the value tile of
-            // the same stage (free when the second product of tile i - kStages is done): keys are asked for one tile ahead
+            // The place of key tile i is free when the scores of tile i - kKeyStages are done, which is earlier than the place
+            // of value tile i (free when the second product of tile i - kValueStages is done): keys are asked for ahead
             // of values, in the order in which their places come free.
             auto load_keys = [&](int i) {
-                const int s = i % kStages;
-                const uint32_t use = i / kStages;
+                const int s = i % kKeyStages;
+                const uint32_t use = i / kKeyStages;
                 if (use > 0 && !barrier_wait(&shared->k_free[s], (use - 1) & 1u, abort_flag)) return false;
                 const int row = (pages[first_tile + i] * n_kv_heads + kv_head) * BN;
                 barrier_expect_bytes(&shared->k_full[s], kKeyBytes);
@@ -297,8 +308,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 return true;
             };
             auto load_values = [&](int i) {
-                const int s = i % kStages;
-                const uint32_t use = i / kStages;
+                const int s = i % kValueStages;
+                const uint32_t use = i / kValueStages;
                 if (use > 0 && !barrier_wait(&shared->v_free[s], (use - 1) & 1u, abort_flag)) return false;
                 const int row = (pages[first_tile + i] * n_kv_heads + kv_head) * BN;
                 barrier_expect_bytes(&shared->v_full[s], kKeyBytes);
@@ -306,12 +317,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     tma_load_2d(value_tiles + s * kKeyBytes + half * (BN * 128), &v_map, half * 64, row, &shared->v_full[s]);
                 return true;
             };
+            // Completion order of the products: scores 0, scores 1, second product 0, scores 2, second product 1, ...; a
+            // load is issued when the product that frees its place is the next to finish, so no wait blocks a later load
+            // whose place is free already: keys run kAhead tiles ahead of values.
+            constexpr int kAhead = kKeyStages - kValueStages + 1;
             bool alive = true;
-            for (int i = 0; i < n_tiles && alive; ++i) {
-                alive = load_keys(i);
-                if (alive && i > 0) alive = load_values(i - 1);
+            for (int i = 0; i < n_tiles + kAhead && alive; ++i) {
+                if (i < n_tiles) alive = load_keys(i);
+                if (alive && i >= kAhead) alive = load_values(i - kAhead);
             }
-            if (alive && n_tiles > 0) load_values(n_tiles - 1);
         }
     } else if (warp == 5) {
         // ---- MMA issuer -----------------------------------------------------------------------------------------
@@ -321,9 +335,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // Scores run one tile ahead of the softmax: while the four warps work on tile i, the products of tile i + 1
             // fill the other score buffer, and the second product of tile i follows as soon as its probabilities are there.
             auto issue_scores = [&](int i) {
-                const int s = i % kStages;
+                const int s = i % kKeyStages;
                 const uint32_t key_address = smem_address(key_tiles + s * kKeyBytes);
-                if (!barrier_wait(&shared->k_full[s], (i / kStages) & 1u, abort_flag)) return false;
+                if (!barrier_wait(&shared->k_full[s], (i / kKeyStages) & 1u, abort_flag)) return false;
                 // The buffer also held the probabilities of tile i - 2; their product was issued before this one and the
                 // tensor core takes products in the order of issue, so only the softmax's read needs waiting for.
                 if (i >= 2 && !barrier_wait(&shared->s_free[i & 1], ((i >> 1) - 1) & 1u, abort_flag)) return false;
@@ -342,9 +356,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             bool alive = barrier_wait(&shared->q_full, 0, abort_flag) && issue_scores(0);
             for (int i = 0; i < n_tiles && alive; ++i) {
                 if (i + 1 < n_tiles && !issue_scores(i + 1)) break;
-                const int s = i % kStages;
+                const int s = i % kValueStages;
                 const uint32_t value_address = smem_address(value_tiles + s * kKeyBytes);
-                if (!barrier_wait(&shared->v_full[s], (i / kStages) & 1u, abort_flag)) break;
+                if (!barrier_wait(&shared->v_full[s], (i / kValueStages) & 1u, abort_flag)) break;
                 // Probabilities lie where the scores of the tile were: 16 keys are 8 columns.
                 if (!barrier_wait(&shared->p_ready[i & 1], (i >> 1) & 1u, abort_flag)) break;
                 tensor_fence_after_sync();
@@ -366,7 +380,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         float used_max = -INFINITY, sum = 0.0f;                   // the maximum that O and `sum` are scaled by
         bool alive = true;
         for (int i = 0; i < n_tiles && alive; ++i) {
-            const int s = i % kStages;
+            const int s = i % kValueStages;
             if (!barrier_wait(&shared->s_full[i & 1], (i >> 1) & 1u, abort_flag)) { alive = false; break; }
             tensor_fence_after_sync();
             float score[BN];
@@ -390,7 +404,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 // probabilities are zero, but zero times a stale NaN is not: clear those value rows before the product.
                 uint8_t* value_tile = value_tiles + s * kKeyBytes;
                 const int first_stale = last_position - key0 + 1;
-                if (!barrier_wait(&shared->v_full[s], (i / kStages) & 1u, abort_flag)) { alive = false; break; }   // the tile must have landed first
+                if (!barrier_wait(&shared->v_full[s], (i / kValueStages) & 1u, abort_flag)) { alive = false; break; }   // the tile must have landed first
                 for (int item = threadIdx.x; item < (BN - first_stale) * kHalves * 8; item += 128) {
                     const int chunk = item % 8, half = (item / 8) % kHalves, stale_row = first_stale + item / (8 * kHalves);
                     *reinterpret_cast<uint4*>(value_tile + half * (BN * 128) + stale_row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -411,11 +425,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // Rescale O and the sum only when the maximum has grown by more than the threshold (or nothing was kept yet).
             float shift = used_max;
             const bool grow = tile_max > used_max + kRescaleThreshold;     // true for the first key a row sees
-            // O must not be touched while the second product of the tile before is still writing it.
-            if (i > 0 && !barrier_wait(&shared->pv_done, (i - 1) & 1u, abort_flag)) { alive = false; break; }
             // The loads and stores of tensor memory are warp-wide, so the whole warp takes part if any of its rows grows.
             const bool rescale = grow && i > 0 && used_max != -INFINITY;
             if (__any_sync(0xffffffffu, rescale)) {
+                // O must not be touched while the second product of the tile before is still writing it.  Only here: a warp
+                // whose maxima have settled never waits for that product, and its exponentials run beside it.  (The
+                // softmax is at most one tile ahead of the second products, so the phase waited for is the current one
+                // or the one just completed.)
+                if (!barrier_wait(&shared->pv_done, (i - 1) & 1u, abort_flag)) { alive = false; break; }
                 tensor_fence_after_sync();
                 const float factor = rescale ? exp2f(used_max - tile_max) : 1.0f;
                 sum *= factor;
@@ -535,7 +552,7 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
     if (!make_map(&q_map, queries, n_tokens, static_cast<long long>(n_heads) * D, BM) || !make_map(&k_map, keys, cache_rows, D, BN) ||
         !make_map(&v_map, values, cache_rows, D, BN))
         return cudaErrorInvalidValue;
-    const int shared_bytes = sizeof(Shared) + 1024 + kQBytes + kStages * kStageBytes;
+    const int shared_bytes = kQBytes + (kKeyStages + kValueStages) * kKeyBytes + static_cast<int>(sizeof(Shared));
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
