@@ -124,6 +124,6 @@ def generate(model, prompts: Sequence[Sequence[int]], max_new_tokens=None, tempe
         stop_tokens = settings.eos_token_ids
     sampler = Sampler(SamplingParams(temperature=temperature, seed=seed))
     metrics = GenerationMetrics()
-    results = generate_tokens(engine, prompts, max_new_tokens, sampler.select, stop_tokens, max_batch,
+    results = generate_tokens(engine, prompts, max_new_tokens, sampler, stop_tokens, max_batch,
                               prefill_chunk_tokens, metrics)
     return GenerateOutput(results, metrics)

@@ -521,6 +521,17 @@ def argmax(logits, tokens, valid) -> None:
                               ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax", 2)
 
 
+def store_words_host(source, pinned_target) -> None:
+    """Writes the int32 words of `source` (device, contiguous) into `pinned_target` (page-locked host memory, contiguous, the
+    same number of words) from a kernel, in stream order; no copy engine takes part."""
+    _require(source.dtype == torch.int32 == pinned_target.dtype and source.is_contiguous() and pinned_target.is_contiguous()
+             and source.numel() == pinned_target.numel() and source.is_cuda and not pinned_target.is_cuda and pinned_target.is_pinned(),
+             "needs contiguous int32 words on the device and as many in page-locked host memory")
+    library = build.load_library("sampling.cu")
+    _check(library.tau_store_words_host(_pointer(source), ctypes.c_void_p(pinned_target.data_ptr()), ctypes.c_int(source.numel()), _stream()),
+           "store_words_host")
+
+
 def sample_gumbel(logits, tokens, valid, inverse_temperature: float, seed: int, request_ids, token_indices) -> None:
     _check_selection(logits, tokens, valid)
     _on_device(request_ids, token_indices)

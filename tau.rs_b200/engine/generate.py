@@ -14,6 +14,14 @@ are more requests than fit, batches run one after another on the same cache.
 
 The loop needs only `open_sequence`, `close_sequence`, `step` and the two limits of a
 backend, and a `select` function, so its decisions can be tested with fakes.
+
+Where the backend takes token ids from the device (`accepts_device_tokens`) and `select`
+comes in two halves (`launch`, `collect`), decoding runs one step ahead of the host: step
+t + 1 is started with the ids that step t chose, straight from the device, and only then
+does the host wait for step t's ids, look for stop tokens and book the results.  A request
+that turns out to have stopped at step t has had one more token computed, which is dropped
+with its slot; a request whose limit the token of step t reaches is left out of step t + 1
+beforehand.  The tokens are the same either way.
 """
 from __future__ import annotations
 
@@ -89,7 +97,7 @@ def plan_batches(needs: Sequence[int], max_batch: int, capacity_tokens: int) -> 
     return batches
 
 
-@dataclass
+@dataclass(eq=False)     # a request in flight is itself, whatever it holds
 class _Live:
     request: int
     slot: int
@@ -192,6 +200,9 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
             accept(item, first_tokens[item.request])
 
         # Decode: one token for every request that is still going.
+        launch, collect = getattr(select, "launch", None), getattr(select, "collect", None)
+        if launch is not None and collect is not None and getattr(backend, "accepts_device_tokens", False):
+            _decode_ahead(backend, live, launch, collect, stop, accept, metrics)
         while live:
             started = time.perf_counter()
             entries = [StepEntry(item.slot, [item.produced[-1]], [0]) for item in live]
@@ -206,3 +217,49 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
     finally:
         for item in list(live):
             backend.close_sequence(item.slot)
+
+
+def _decode_ahead(backend, live, launch, collect, stop, accept, metrics) -> None:
+    """The decode loop, one step ahead of the host; returns with `live` empty."""
+    if not live:
+        return
+    started = time.perf_counter()
+    # The first step takes its tokens from the host (the prefill chose them).
+    items = list(live)
+    logits = backend.step([StepEntry(item.slot, [item.produced[-1]], [0]) for item in items])
+    pending = launch(logits, [item.request for item in items], [len(item.produced) for item in items])
+    metrics.decode_steps += 1
+    while True:
+        # Who goes on after the token that is on its way?  Not those whose limit it reaches; the others do, unless it
+        # turns out to be a stop token, which is known only after their next step has been started.
+        # (A request of `items` that stopped at the step before is still in `items`, for its row, but no longer in `live`.)
+        rows = [row for row, item in enumerate(items) if item in live and len(item.produced) + 1 < item.limit]
+        following = None
+        if rows:
+            next_items = [items[row] for row in rows]
+            tokens_on_device = pending.tokens if len(rows) == len(items) else _take(pending.tokens, rows)
+            logits = backend.step([StepEntry(item.slot, [0], [0]) for item in next_items], device_tokens=tokens_on_device)
+            following = launch(logits, [item.request for item in next_items], [len(item.produced) + 1 for item in next_items])
+            metrics.decode_steps += 1
+        tokens = collect(pending)
+        for item, token in zip(items, tokens):
+            if item not in live:      # stopped one step ago; this token was computed for nothing
+                continue
+            if token not in stop:
+                metrics.decode_tokens += 1
+            accept(item, token)
+        if following is None:
+            break
+        items, pending = next_items, following
+    metrics.decode_ms += (time.perf_counter() - started) * 1e3
+
+
+def _take(tokens, rows):
+    """The entries `rows` (ascending) of the ids that a step chose, where they are: a device tensor, or a fake's list."""
+    if isinstance(tokens, list):
+        return [tokens[row] for row in rows]
+    if rows == list(range(rows[0], rows[-1] + 1)):
+        return tokens[rows[0] : rows[-1] + 1]
+    import torch
+
+    return tokens.index_select(0, torch.tensor(rows, dtype=torch.int64, device=tokens.device))

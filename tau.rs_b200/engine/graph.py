@@ -57,7 +57,7 @@ class _DecodeGraph:
             staged[begin : begin + n * stride] = cache.page_rows(group, slots, stride).reshape(-1)
 
 
-def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]):
+def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int], device_tokens=None):
     max_len = max(starts) + 1
     bucket = (len(entries), max(0, (max_len - 1).bit_length()))
     splits = engine._split_choice.get(bucket)
@@ -72,6 +72,8 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
     state.fill(staged, entries, starts, engine.cache)
     engine.ring(state.layout.total).upload(ticket, state.layout.total, state.buffer)
     context = state.context
+    if device_tokens is not None:   # after the upload, in stream order: the ids that an earlier kernel chose
+        context.token_ids.copy_(device_tokens)
     context.max_len = max_len
     if state.graph is None:
         # Warm-up outside capture: compiles and loads every kernel, sizes torch's pools.

@@ -70,6 +70,8 @@ class Engine:
         return self.cache.max_sequence_tokens
 
     # ---- the step ----------------------------------------------------------------
+    accepts_device_tokens = True   # `step(entries, device_tokens=...)`
+
     def _validate(self, entries: Sequence[StepEntry]) -> List[int]:
         if not entries:
             raise StepError("a step needs at least one sequence")
@@ -129,18 +131,28 @@ class Engine:
             buffer.copy_(torch.from_numpy(staged))
         return step_views(layout, buffer, max_new, max_len, all(len(entry.tokens) == 1 for entry in entries))
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries' tokens; returns 32-bit logits `[wanted places, vocab]` in the order of the
-        entries and of their `want`, or None if nothing is wanted."""
+        entries and of their `want`, or None if nothing is wanted.
+
+        `device_tokens` (int32, one per entry, on the engine's device) replaces the token ids of a step in which every
+        entry brings one token: the ids are taken on the device, in stream order, so a step can be started before the
+        host has seen what the step before it chose.  An id outside the vocabulary embeds as zeros."""
         starts = self._validate(entries)
+        if device_tokens is not None and (any(len(entry.tokens) != 1 for entry in entries) or device_tokens.numel() != len(entries)
+                                          or device_tokens.dtype != torch.int32 or device_tokens.device != self.device):
+            raise StepError("device tokens need one int32 id per entry on the engine's device, and one token per entry")
         for entry, start in zip(entries, starts):
             self.cache.reserve(entry.slot, start + len(entry.tokens))
         single = all(len(entry.tokens) == 1 and tuple(entry.want) == (0,) for entry in entries)
         if single and self.use_graphs:
             from .graph import run_decode_graph
-            logits = run_decode_graph(self, entries, starts)
+            logits = run_decode_graph(self, entries, starts, device_tokens)
         else:
-            logits = self.model.forward(self._context(entries, starts), self.cache)
+            context = self._context(entries, starts)
+            if device_tokens is not None:
+                context.token_ids.copy_(device_tokens)
+            logits = self.model.forward(context, self.cache)
         for entry, start in zip(entries, starts):
             self.cache.advance(entry.slot, start + len(entry.tokens))
         return logits

@@ -34,12 +34,30 @@ class AllLogitsNaN(RuntimeError):
     pass
 
 
+class Pending:
+    """Tokens that have been chosen on the device and are on their way to the host."""
+
+    def __init__(self, result: torch.Tensor, host: torch.Tensor, done):
+        self.result = result          # [2, rows] on the device: token ids, and whether the row had a number to choose from
+        self.host = host              # the same, on the host (pinned), valid once `done` has passed
+        self.done = done              # an event, or None where the copy was synchronous
+
+    @property
+    def tokens(self) -> torch.Tensor:
+        """The chosen ids on the device, for a step that starts before the host has seen them."""
+        return self.result[0]
+
+
 class Sampler:
+    """`select` chooses and waits; `launch` and `collect` are its two halves, so that a caller can put more work
+    on the device between them: the host waits for the event behind the copy of the tokens, not for the stream."""
+
     def __init__(self, params: SamplingParams = SamplingParams()):
         self.params = params
+        self._pinned = {}
+        self._next = 0
 
-    def select(self, logits: torch.Tensor, request_ids: Sequence[int], token_indices: Sequence[int]) -> List[int]:
-        """One token for each row of `logits` `[rows, vocab]`; blocks until the tokens are on the host."""
+    def launch(self, logits: torch.Tensor, request_ids: Sequence[int], token_indices: Sequence[int]) -> Pending:
         rows = logits.shape[0]
         result = torch.empty((2, rows), dtype=torch.int32, device=logits.device)
         if self.params.temperature == 0.0:
@@ -47,7 +65,32 @@ class Sampler:
         else:
             keys = torch.tensor([list(request_ids), list(token_indices)], dtype=torch.int32).to(logits.device)
             kernels.sample_gumbel(logits, result[0], result[1], 1.0 / self.params.temperature, self.params.seed, keys[0], keys[1])
-        tokens, valid = result.cpu().tolist()
+        if logits.device.type != "cuda":
+            return Pending(result, result, None)
+        if (rows, logits.device) not in self._pinned:
+            self._pinned[(rows, logits.device)] = [torch.empty((2, rows), dtype=torch.int32).pin_memory() for _ in range(4)]
+        ring = self._pinned[(rows, logits.device)]
+        host = ring[self._next % len(ring)]
+        self._next += 1
+        # A kernel stores the tokens into page-locked host memory (a copy by the copy engine in this stream held the next
+        # step up by 80 us) and an event marks it: work put on the stream afterwards (the next step) does not hold up the
+        # host's wait for these tokens.
+        kernels.store_words_host(result, host)
+        done = torch.cuda.Event()
+        done.record()
+        return Pending(result, host, done)
+
+    def collect(self, pending: Pending) -> List[int]:
+        """Blocks until the tokens of `pending` are on the host."""
+        if pending.done is not None:
+            pending.done.synchronize()
+        tokens, valid = pending.host.tolist()
         if not all(valid):
             raise AllLogitsNaN("model logits are all NaN")
         return tokens
+
+    def select(self, logits: torch.Tensor, request_ids: Sequence[int], token_indices: Sequence[int]) -> List[int]:
+        """One token for each row of `logits` `[rows, vocab]`; blocks until the tokens are on the host."""
+        return self.collect(self.launch(logits, request_ids, token_indices))
+
+    __call__ = select

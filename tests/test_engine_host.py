@@ -93,3 +93,24 @@ def test_step_refuses_bad_entries(cpu_kernels, folders):
     assert engine.cache.free_tokens() == 128
     assert engine.step([StepEntry(slot, [1, 2, 3], [])]) is None
     assert engine.sequence_length(slot) == 3
+
+
+def test_generation_one_step_ahead_equals_step_by_step(cpu_kernels, folders):
+    """`generate` through the engine and the sampler's two halves (decoding one step ahead of the host) against the same
+    loop with a plain `select` function: stop tokens in the middle, unequal limits, more requests than one batch holds."""
+    from tau_rs_b200 import Sampler
+    from tau_rs_b200.engine import generate_tokens
+
+    vocab = tiny_configs.CONFIGS["A"]["vocab_size"]
+    prompts = random_prompts(vocab, [5, 1, 33, 70, 9], seed=21)
+    limits = [12, 1, 7, 20, 3]
+    sampler = Sampler()
+    step_by_step = generate_tokens(engine_for(folders["A"], "float32", "cpu", max_tokens=64 * 6), prompts, limits,
+                                   lambda logits, requests, indices: sampler.select(logits, requests, indices), max_batch=3)
+    for stop in ((), tuple(step_by_step[3].tokens[4:6])):
+        plain = generate_tokens(engine_for(folders["A"], "float32", "cpu", max_tokens=64 * 6), prompts, limits,
+                                lambda logits, requests, indices: sampler.select(logits, requests, indices), stop_tokens=stop, max_batch=3)
+        engine = engine_for(folders["A"], "float32", "cpu", max_tokens=64 * 6)
+        ahead = generate_tokens(engine, prompts, limits, sampler, stop_tokens=stop, max_batch=3)
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+        engine.cache.check()

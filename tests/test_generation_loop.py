@@ -130,3 +130,79 @@ def test_slots_are_given_back_when_a_step_fails():
         assert backend.open == set() and sorted(backend.opened) == sorted(backend.closed)
         backend.fail_at_step = None
         assert generate_tokens(backend, [[4, 4]], 2, select)[0].tokens == expected_tokens([4, 4], 2)   # no retry needed, the next request works
+
+
+# ---- one step ahead of the host ---------------------------------------------------------------------
+class AheadBackend(FakeBackend):
+    """Also takes the tokens of a step from "the device" (here: a list that the fake `launch` handed out)."""
+    accepts_device_tokens = True
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.from_device = []
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            assert len(device_tokens) == len(entries) and all(len(entry.tokens) == 1 for entry in entries)
+            self.from_device.append(list(device_tokens))
+        return super().step(entries)
+
+
+class Handle:
+    def __init__(self, rows):
+        self.tokens = list(rows)
+
+
+class TwoHalves:
+    """A `select` in two halves; `collected` counts how many steps the host has seen the tokens of."""
+
+    def __init__(self):
+        self.launched, self.collected, self.order = 0, 0, []
+
+    def launch(self, rows, request_ids, token_indices):
+        self.launched += 1
+        self.order.append(("launch", list(request_ids), list(token_indices)))
+        return Handle(rows)
+
+    def collect(self, handle):
+        self.collected += 1
+        self.order.append(("collect",))
+        return list(handle.tokens)
+
+    def __call__(self, rows, request_ids, token_indices):
+        return self.collect(self.launch(rows, request_ids, token_indices))
+
+
+@pytest.mark.parametrize("stop", [(), (9,), (7, 30)])
+def test_one_step_ahead_gives_the_same_tokens_and_reasons(stop):
+    prompts = [[3, 4, 5], [20], [7] * 10, [41, 2]]
+    limits = [6, 1, 12, 4]
+    plain = generate_tokens(FakeBackend(), prompts, limits, select, stop_tokens=stop)
+    backend, halves = AheadBackend(), TwoHalves()
+    ahead = generate_tokens(backend, prompts, limits, halves, stop_tokens=stop)
+    assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+    assert not backend.open and sorted(backend.closed) == sorted(backend.opened)      # every slot given back once
+
+
+def test_one_step_ahead_starts_the_next_step_before_it_reads_the_last():
+    backend, halves = AheadBackend(), TwoHalves()
+    results = generate_tokens(backend, [[1, 2], [5]], [4, 2], halves)
+    assert [r.tokens for r in results] == [expected_tokens([1, 2], 4), expected_tokens([5], 2)]
+    # After the prefill (one launch and its collect): launch of decode step 1, launch of step 2, then the collect of step 1.
+    decode = halves.order[2:]
+    assert [event[0] for event in decode[:3]] == ["launch", "launch", "collect"]
+    # Request 1 reaches its limit of 2 with the token of decode step 1: it is not in step 2.
+    assert decode[0][1] == [0, 1] and decode[1][1] == [0]
+    # Token indices: the token being chosen is one further than what the host has booked.
+    assert decode[0][2] == [1, 1] and decode[1][2] == [2]
+    assert len(backend.from_device) == 2 and all(len(tokens) == 1 for tokens in backend.from_device)
+
+
+def test_one_step_ahead_drops_the_token_computed_past_a_stop():
+    # Request 0 yields 3, 4, 5, ...; 5 is a stop token.  Its step after the 5 has been started already and is thrown away.
+    backend, halves = AheadBackend(), TwoHalves()
+    results = generate_tokens(backend, [[1, 2, 3], [10]], [8, 8], halves, stop_tokens=(5,))
+    assert results[0].tokens == [3, 4] and results[0].finish_reason == "stop"
+    assert results[1].tokens == expected_tokens([10], 8) and results[1].finish_reason == "length"
+    slot0_steps = [step for step in backend.steps if any(entry[0] == backend.opened[0] for entry in step)]
+    assert len(slot0_steps) == 1 + 3       # the prompt, the steps fed 3 and 4, and the one fed 5 for nothing
