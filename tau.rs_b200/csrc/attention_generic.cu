@@ -118,47 +118,60 @@ __global__ void attention_prepare_vec_kernel(
             sines[i] = sin_table[table + i];
         }
     }
-    for (int head = warp; head < heads_total; head += warps) {
-        const Vector loaded = *reinterpret_cast<const Vector*>(row + static_cast<size_t>(head) * head_dim + PER * lane);
-        T* target;
-        const float* weight;
-        if (head < n_heads) {
-            target = queries + (static_cast<size_t>(token) * n_heads + head) * head_dim;
-            weight = q_weight;
-        } else {
-            const int kv_head = (head - n_heads) % n_kv_heads;
-            const bool is_key = head < n_heads + n_kv_heads;
-            target = (is_key ? keys : values) + cache_base + static_cast<size_t>(kv_head) * page_tokens * head_dim;
-            weight = k_weight;
-            if (!is_key) {  // values are stored as projected
-                *reinterpret_cast<Vector*>(target + PER * lane) = loaded;
-                continue;
+    // A warp takes the heads warp, warp + warps, ...; their vectors are asked for several at a time, so that the loads of
+    // one token's heads travel together instead of one after another.
+    constexpr int kBatch = 6;
+    for (int first = warp; first < heads_total; first += warps * kBatch) {
+        Vector loaded[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int head = first + b * warps;
+            if (head < heads_total) loaded[b] = *reinterpret_cast<const Vector*>(row + static_cast<size_t>(head) * head_dim + PER * lane);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int head = first + b * warps;
+            if (head >= heads_total) break;
+            T* target;
+            const float* weight;
+            if (head < n_heads) {
+                target = queries + (static_cast<size_t>(token) * n_heads + head) * head_dim;
+                weight = q_weight;
+            } else {
+                const int kv_head = (head - n_heads) % n_kv_heads;
+                const bool is_key = head < n_heads + n_kv_heads;
+                target = (is_key ? keys : values) + cache_base + static_cast<size_t>(kv_head) * page_tokens * head_dim;
+                weight = k_weight;
+                if (!is_key) {  // values are stored as projected
+                    *reinterpret_cast<Vector*>(target + PER * lane) = loaded[b];
+                    continue;
+                }
             }
-        }
-        float value[PER];
+            float value[PER];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) value[i] = to_float(loaded.v[i]);
-        if (weight) {
-            float squares = 0.0f;
+            for (int i = 0; i < PER; ++i) value[i] = to_float(loaded[b].v[i]);
+            if (weight) {
+                float squares = 0.0f;
 #pragma unroll
-            for (int i = 0; i < PER; ++i) squares += value[i] * value[i];
-            const float inverse = rsqrtf(warp_sum(squares) / static_cast<float>(head_dim) + eps);
+                for (int i = 0; i < PER; ++i) squares += value[i] * value[i];
+                const float inverse = rsqrtf(warp_sum(squares) / static_cast<float>(head_dim) + eps);
 #pragma unroll
-            for (int i = 0; i < PER; ++i) value[i] = round_through<T>(value[i] * inverse * weight[PER * lane + i]);
-        }
-        Vector result;
-        if (rotary_dim) {
-#pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                const float partner = __shfl_xor_sync(0xffffffffu, value[i], 16);
-                // first half: x cos - partner sin; second half: x cos + partner sin
-                result.v[i] = from_float<T>(lane < 16 ? value[i] * cosines[i] - partner * sines[i] : value[i] * cosines[i] + partner * sines[i]);
+                for (int i = 0; i < PER; ++i) value[i] = round_through<T>(value[i] * inverse * weight[PER * lane + i]);
             }
-        } else {
+            Vector result;
+            if (rotary_dim) {
 #pragma unroll
-            for (int i = 0; i < PER; ++i) result.v[i] = from_float<T>(value[i]);
+                for (int i = 0; i < PER; ++i) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, value[i], 16);
+                    // first half: x cos - partner sin; second half: x cos + partner sin
+                    result.v[i] = from_float<T>(lane < 16 ? value[i] * cosines[i] - partner * sines[i] : value[i] * cosines[i] + partner * sines[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) result.v[i] = from_float<T>(value[i]);
+            }
+            *reinterpret_cast<Vector*>(target + PER * lane) = result;
         }
-        *reinterpret_cast<Vector*>(target + PER * lane) = result;
     }
 }
 
