@@ -114,3 +114,24 @@ def test_generation_one_step_ahead_equals_step_by_step(cpu_kernels, folders):
         ahead = generate_tokens(engine, prompts, limits, sampler, stop_tokens=stop, max_batch=3)
         assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
         engine.cache.check()
+
+
+def test_step_takes_token_ids_from_the_device_or_refuses_them(cpu_kernels, folders):
+    vocab = tiny_configs.CONFIGS["B"]["vocab_size"]
+    (tokens,) = random_prompts(vocab, [20], seed=8)
+    wanted = plain_logits(folders["B"], tokens)
+    engine = engine_for(folders["B"], "float32", "cpu")
+    slot = engine.open_sequence()
+    engine.step([StepEntry(slot, tokens[:19], [])])
+    # The id comes from a tensor; the entry's own token is a placeholder.
+    logits = engine.step([StepEntry(slot, [0], [0])], device_tokens=torch.tensor([tokens[19]], dtype=torch.int32))
+    assert relative_error(logits, wanted[19:20]) < 1e-4
+    length = engine.sequence_length(slot)
+    for entries, ids in (([StepEntry(slot, [0, 0], [1])], torch.tensor([1, 2], dtype=torch.int32)),      # two tokens in one entry
+                         ([StepEntry(slot, [0], [0])], torch.tensor([1, 2], dtype=torch.int32)),          # one id too many
+                         ([StepEntry(slot, [0], [0])], torch.tensor([1], dtype=torch.int64))):            # not int32
+        with pytest.raises(StepError):
+            engine.step(entries, device_tokens=ids)
+        assert engine.sequence_length(slot) == length      # refused before anything changed
+    engine.close_sequence(slot)
+    engine.cache.check()
