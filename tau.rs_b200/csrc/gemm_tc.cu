@@ -188,7 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
     constexpr uint32_t kWeightBytes = BM * BK * 2, kInputBytes = BN * BK * 2, kStageBytes = kWeightBytes + kInputBytes;
-    constexpr uint32_t kColumns = 2 * BN < 32 ? 32 : 2 * BN;   // two accumulators; a power of two of at least 32
+    constexpr uint32_t kColumns = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;   // two accumulators; a power of two of at least 32
     float* const own_partial = reinterpret_cast<float*>(tiles);   // clustered: [token][BM] floats over the stages, once they are done with
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -849,6 +849,7 @@ int dispatch(const CUtensorMap& weight_map, const CUtensorMap& input_map, int bo
         case 32: return launch<32, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
         case 64: return launch<64, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
         case 128: return launch<128, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
+        case 192: return launch<192, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
         default: return launch<256, TOut, Gated>(weight_map, input_map, bias, out, M, N, K, out_stride, plan, stream);
     }
 }
@@ -878,12 +879,29 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
     const SplitPlan plan{splits, static_cast<float*>(workspace), workspace_floats, static_cast<int*>(tickets), cluster};
     int box = token_box;
     if (box == 0) box = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    if (box != 16 && box != 32 && box != 64 && box != 128 && box != 256) return cudaErrorInvalidValue;
+    if (box != 16 && box != 32 && box != 64 && box != 128 && box != 192 && box != 256) return cudaErrorInvalidValue;
     if (pair > 0 && (box != 256 || splits > 1)) return cudaErrorInvalidValue;
     bool paired = box == 256 && pair != 0 && splits <= 1;   // a cut along K is run on single SMs, whether asked for or chosen
     if (paired && pair < 0 && splits == 0 && workspace && tickets) {
-        const int tiles = ((N + BM - 1) / BM) * ((M + 255) / 256);
-        if (choose_splits(M, tiles, (K + BK - 1) / BK, sm_count(), workspace_floats, 256 * BM) > 1) paired = false;
+        const int feature_tiles = (N + BM - 1) / BM, tiles = feature_tiles * ((M + 255) / 256);
+        if (choose_splits(M, tiles, (K + BK - 1) / BK, sm_count(), workspace_floats, 256 * BM) > 1) {
+            paired = false;
+        } else if (token_box == 0) {
+            // Between the batches that are cut along K and the prompts that fill every SM several times, the token tile
+            // decides how many SMs have work: 512 tokens of a 6144-feature product are 96 tiles of 256 tokens, but 144
+            // of 192.  An estimate of waves x (tokens of a tile + a fixed part) picks among 256, 192 and 128.
+            int best = 256;
+            long long best_cost = 0;
+            for (int candidate : {256, 192, 128}) {
+                const long long count = static_cast<long long>(feature_tiles) * ((M + candidate - 1) / candidate);
+                const long long cost = ((count + sm_count() - 1) / sm_count()) * (candidate + 64);
+                if (candidate == 256 || cost < best_cost) { best = candidate; best_cost = cost; }
+            }
+            if (best != 256) {
+                box = best;
+                paired = false;
+            }
+        }
     }
     CUtensorMap weight_map, input_map;
     if (!make_map(&weight_map, w, N, K, w_stride, BM) || !make_map(&input_map, x, M, K, x_stride, paired ? kPairHalf : box)) return cudaErrorInvalidValue;

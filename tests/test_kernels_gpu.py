@@ -109,7 +109,7 @@ def test_gemm_skinny(out_dtype, m, n, k):
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("m,n,k,box", [(1, 8, 8, 0), (16, 128, 64, 0), (33, 130, 72, 0), (128, 128, 128, 0), (200, 300, 200, 0),
                                        (257, 129, 520, 0), (700, 260, 1032, 0), (40, 500, 96, 16), (100, 257, 136, 32),
-                                       (300, 100, 64, 128), (64, 1000, 224, 256)])
+                                       (300, 100, 64, 128), (64, 1000, 224, 256), (500, 260, 136, 192), (193, 129, 72, 192), (512, 6144, 256, 0), (1024, 700, 64, 0)])
 def test_gemm_tc(out_dtype, m, n, k, box):
     """The tcgen05 product at ragged sizes (zero-filled tails in every direction), every token tile, strided views."""
     values = randn(m, k + 8, dtype=torch.bfloat16, seed=18)[:, :k]
