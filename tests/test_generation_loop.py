@@ -206,3 +206,25 @@ def test_one_step_ahead_drops_the_token_computed_past_a_stop():
     assert results[1].tokens == expected_tokens([10], 8) and results[1].finish_reason == "length"
     slot0_steps = [step for step in backend.steps if any(entry[0] == backend.opened[0] for entry in step)]
     assert len(slot0_steps) == 1 + 3       # the prompt, the steps fed 3 and 4, and the one fed 5 for nothing
+
+
+def test_one_step_ahead_equals_step_by_step_on_random_requests():
+    """Many random mixes of prompts, limits, stop tokens, batch sizes and prefill chunks: the loop that runs ahead returns what
+    the plain loop returns, gives every slot back once, and never steps a request that has ended."""
+    import random
+
+    rng = random.Random(7)
+    for trial in range(200):
+        count = rng.randint(1, 7)
+        prompts = [[rng.randrange(50) for _ in range(rng.randint(1, 12))] for _ in range(count)]
+        limits = [rng.randint(0, 9) for _ in range(count)]
+        stop = tuple(rng.sample(range(50), rng.randint(0, 6)))
+        max_batch = rng.randint(1, 4)
+        chunk = rng.choice([None, 1, 3, 8])
+        plain = generate_tokens(FakeBackend(), prompts, limits, select, stop_tokens=stop, max_batch=max_batch, prefill_chunk_tokens=chunk)
+        backend, metrics = AheadBackend(), GenerationMetrics()
+        ahead = generate_tokens(backend, prompts, limits, TwoHalves(), stop_tokens=stop, max_batch=max_batch, prefill_chunk_tokens=chunk,
+                                metrics=metrics)
+        assert [(r.tokens, r.finish_reason, r.prompt_tokens) for r in ahead] == [(r.tokens, r.finish_reason, r.prompt_tokens) for r in plain], trial
+        assert not backend.open and sorted(backend.closed) == sorted(backend.opened)
+        assert metrics.generated_tokens == sum(len(r.tokens) for r in ahead)
