@@ -335,12 +335,14 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Four blocks of the
     decode kernel fit an SM, so the aim is the largest number of splits whose blocks are all resident at once
     (one wave: a second, partly filled wave costs more than the extra parallelism gives), each split at least 64
-    positions long.  The length is rounded up to a power of two first, so that a captured graph (whose key holds
-    this number) serves a whole range of lengths.
+    positions long, and at most 16 splits up to 4,096 positions, 32 beyond (one sequence of 2,049 positions: 11.8 us
+    with 16 splits, 13.8 us with 32; of 32,001: 39.8 us with 32, 54.4 us with 16; the last block's merge grows with
+    the splits).  The length is rounded up to a power of two first, so that a captured graph (whose key holds this
+    number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
     wanted = max(1, 592 // max(1, n_seqs * kv_blocks))
-    return max(1, min(wanted, bucket // 64, 32))
+    return max(1, min(wanted, bucket // 64, 16 if bucket <= 4096 else 32))
 
 
 _decode_scratch = {}
