@@ -301,11 +301,13 @@ __global__ void __launch_bounds__(kWarps * 32, TAU_DECODE_MIN_BLOCKS)
 decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ keys, bf16* __restrict__ values,
                           bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml, int* __restrict__ tickets,
                           const int* __restrict__ seq_len, const int* __restrict__ page_rows, int page_stride, int page_tokens,
-                          int n_heads, int n_kv_heads, int passes, float scale, int window, int splits, DecodePrepare prepare) {
+                          int n_heads, int n_kv_heads, int passes, float scale, int window, int splits, DecodePrepare prepare,
+                          int clustered) {
     grid_dependents_launch();
     grid_dependency_wait();
     __shared__ float merge_o[kWarps][GH][D];
     __shared__ float merge_ml[kWarps][GH][2];
+    __shared__ float block_ml[GH][2];        // clustered: this block's maximum (log2 units) and sum per head
     __shared__ __align__(16) bf16 q_shared[GH][D];
     __shared__ int is_last_block;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -503,6 +505,12 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
             }
             if (splits == 1) {
                 out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
+            } else if (clustered) {
+                merge_o[0][h][c] = o;   // this thread alone reads and writes (h, c) of the first warp's buffer
+                if (c == 0) {
+                    block_ml[h][0] = total_max;
+                    block_ml[h][1] = sum;
+                }
             } else {
                 const size_t slot = record + static_cast<size_t>(h) * splits;
                 partial_o[slot * D + c] = o;
@@ -512,11 +520,58 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
                 }
             }
         }
+    } else if (splits > 1 && clustered) {
+        if (threadIdx.x < heads_here) {
+            block_ml[threadIdx.x][0] = -INFINITY;
+            block_ml[threadIdx.x][1] = 0.0f;
+        }
     } else if (splits > 1 && threadIdx.x < heads_here) {   // nothing for this split: an empty record
         partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2] = -INFINITY;
         partial_ml[(record + static_cast<size_t>(threadIdx.x) * splits) * 2 + 1] = 0.0f;
     }
     if (splits == 1) return;
+    if (clustered) {
+        // The splits of one sequence and KV head are one thread-block cluster: their results stay in shared memory, the
+        // blocks meet, and each merges and stores a share of the heads' columns, reading the others' results through
+        // distributed shared memory in the order of the splits.  Every thread of every block reaches both meetings.
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const unsigned rank = blockIdx.x;   // the cluster spans the grid's x
+        for (int index = rank * (kWarps * 32) + threadIdx.x; index < heads_here * D; index += splits * kWarps * 32) {
+            const int h = index / D, c = index % D;
+            const unsigned o_address = static_cast<unsigned>(__cvta_generic_to_shared(&merge_o[0][h][c]));
+            const unsigned ml_address = static_cast<unsigned>(__cvta_generic_to_shared(&block_ml[h][0]));
+            float split_max[8], split_sum[8], split_o[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                split_max[s] = -INFINITY;
+                split_sum[s] = 0.0f;
+                split_o[s] = 0.0f;
+                if (s < splits) {
+                    unsigned remote_ml, remote_o;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_ml) : "r"(ml_address), "r"(s));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_o) : "r"(o_address), "r"(s));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(split_max[s]) : "r"(remote_ml) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(split_sum[s]) : "r"(remote_ml + 4) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(split_o[s]) : "r"(remote_o) : "memory");
+                }
+            }
+            float total_max = -INFINITY;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) total_max = fmaxf(total_max, split_max[s]);
+            float o = 0.0f, sum = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float factor = exp2f(split_max[s] - total_max);   // 0 for an empty split, whose context is not used
+                if (factor > 0.0f) {
+                    o += split_o[s] * factor;
+                    sum += split_sum[s] * factor;
+                }
+            }
+            out[(static_cast<size_t>(seq) * n_heads + head0 + h) * D + c] = __float2bfloat16_rn(o / sum);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");   // nobody leaves while its results are read
+        return;
+    }
     // The block that finishes last for this sequence and KV head merges the splits' records
     // (the reference's `combine_attention`, decode_attention.cu:255-278, without a launch of its own).
     __threadfence();
@@ -611,7 +666,7 @@ TAU_EXPORT int tau_attention_decode(const void* queries, void* keys, void* value
                                     float scale, int window, int splits, float* scratch, long long scratch_floats, int* tickets,
                                     const void* projected, long long projected_stride, const float* q_weight, const float* k_weight,
                                     float eps, const float* cos_table, const float* sin_table, int rotary_dim, int write_cache,
-                                    void* stream) {
+                                    int cluster_merge, void* stream) {
     if (n_seqs <= 0) return 0;
     if ((!queries && !projected) || !keys || !values || !out || !seq_len || !page_rows || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads != 0 || page_tokens <= 0 || window < 0 || splits < 1 || splits > 256 ||
@@ -632,10 +687,17 @@ TAU_EXPORT int tau_attention_decode(const void* queries, void* keys, void* value
     // Launched after the previous kernel has finished, not beside it: blocks that start on SMs which still hold the
     // blocks of the projection before them (100 KB of shared memory each) ran the whole kernel a half slower at batch 64
     // (138 us against 92 us per layer at 2,048 tokens of context), and at batch 8 starting early gained nothing.
-#define TAU_LAUNCH(GH)                                                                                                             \
-    tau_launch_as(false, decode_partial_mma_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(queries), static_cast<bf16*>(keys), \
-               static_cast<bf16*>(values), static_cast<bf16*>(out), partial_o, partial_ml, tickets, seq_len, page_rows, page_stride,  \
-               page_tokens, n_heads, n_kv_heads, passes, scale, window, splits, prepare)
+    // Up to 8 splits form a thread-block cluster and merge through shared memory; more meet in global memory by tickets.
+    const bool clustered = splits > 1 && splits <= 8 && cluster_merge != 0;
+#define TAU_LAUNCH(GH) do {                                                                                                        \
+    if (clustered)                                                                                                                  \
+        tau_launch_clusters_as(false, splits, decode_partial_mma_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(queries),       \
+                               static_cast<bf16*>(keys), static_cast<bf16*>(values), static_cast<bf16*>(out), partial_o, partial_ml, tickets, seq_len, \
+                               page_rows, page_stride, page_tokens, n_heads, n_kv_heads, passes, scale, window, splits, prepare, 1);   \
+    else                                                                                                                            \
+        tau_launch_as(false, decode_partial_mma_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(queries), static_cast<bf16*>(keys), \
+                      static_cast<bf16*>(values), static_cast<bf16*>(out), partial_o, partial_ml, tickets, seq_len, page_rows, page_stride,  \
+                      page_tokens, n_heads, n_kv_heads, passes, scale, window, splits, prepare, 0); } while (0)
     if (gh == 1) TAU_LAUNCH(1);
     else if (gh == 2) TAU_LAUNCH(2);
     else if (gh == 4) TAU_LAUNCH(4);

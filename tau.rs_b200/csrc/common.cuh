@@ -88,8 +88,8 @@ static inline int tau_launch_as(bool dependent, void (*kernel)(Parameters...), d
 
 // The same with thread-block clusters of `cluster` blocks along x (the grid's x must be a multiple of it).
 template <typename... Parameters, typename... Arguments>
-static inline int tau_launch_clusters(unsigned cluster, void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes,
-                                      cudaStream_t stream, Arguments&&... arguments) {
+static inline int tau_launch_clusters_as(bool dependent, unsigned cluster, void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes,
+                                         cudaStream_t stream, Arguments&&... arguments) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
@@ -103,8 +103,14 @@ static inline int tau_launch_clusters(unsigned cluster, void (*kernel)(Parameter
     attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = tau_dependent_launch_enabled() ? 2 : 1;
+    config.numAttrs = (dependent && tau_dependent_launch_enabled()) ? 2 : 1;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, Parameters(std::forward<Arguments>(arguments))...));
+}
+
+template <typename... Parameters, typename... Arguments>
+static inline int tau_launch_clusters(unsigned cluster, void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes,
+                                      cudaStream_t stream, Arguments&&... arguments) {
+    return tau_launch_clusters_as(true, cluster, kernel, grid, block, shared_bytes, stream, std::forward<Arguments>(arguments)...);
 }
 
 // Launches `kernel` so that it may begin before the previous kernel of the stream has finished.

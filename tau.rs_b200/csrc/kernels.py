@@ -335,14 +335,15 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Four blocks of the
     decode kernel fit an SM, so the aim is the largest number of splits whose blocks are all resident at once
     (one wave: a second, partly filled wave costs more than the extra parallelism gives), each split at least 64
-    positions long, and at most 16 splits up to 4,096 positions, 32 beyond (one sequence of 2,049 positions: 11.8 us
-    with 16 splits, 13.8 us with 32; of 32,001: 39.8 us with 32, 54.4 us with 16; the last block's merge grows with
-    the splits).  The length is rounded up to a power of two first, so that a captured graph (whose key holds this
-    number) serves a whole range of lengths.
+    positions long.  Up to 8 splits merge inside a thread-block cluster, through shared memory, which saves 2 to 5 us
+    against the meeting in global memory; so up to 4,096 positions no more than 8 are used (one sequence of 2,049
+    positions: 11.4 us with 8 splits in a cluster, 12.0 us with 16, 13.8 us with 32), beyond that up to 32 (one sequence
+    of 32,001 positions: 39.8 us with 32, 54.4 us with 16).  The length is rounded up to a power of two first, so that
+    a captured graph (whose key holds this number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
     wanted = max(1, 592 // max(1, n_seqs * kv_blocks))
-    return max(1, min(wanted, bucket // 64, 16 if bucket <= 4096 else 32))
+    return max(1, min(wanted, bucket // 64, 8 if bucket <= 4096 else 32))
 
 
 _decode_scratch = {}
@@ -350,12 +351,14 @@ _decode_tickets = {}
 
 
 def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                     window: int, splits: int, prepare=None) -> None:
+                     window: int, splits: int, prepare=None, cluster_merge: bool = True) -> None:
     """One query token per sequence (its last position) over `seq_len` cached positions, split along the context.
 
     `prepare` (bfloat16 only) is `(projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache)`: the kernel
     then takes queries, the newest key and the newest value from the stacked projection itself (per-head norm,
     rotation, cache write), `queries` may be None, and no prepare kernel is needed before it.
+    `cluster_merge` (bfloat16): up to 8 splits are one thread-block cluster and merge through shared memory; False makes
+    them meet in global memory like larger numbers of splits.
     """
     _on_device(queries, keys, values, out, seq_len, page_rows)
     n_seqs = out.shape[0]
@@ -410,7 +413,8 @@ def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: in
         ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(splits), _pointer(scratch),
         ctypes.c_longlong(0 if scratch is None else scratch.numel()), _pointer(tickets),
         _pointer(projected), ctypes.c_longlong(0 if projected is None else projected.stride(0)), _pointer(q_weight), _pointer(k_weight),
-        ctypes.c_float(eps), _pointer(cos), _pointer(sin), ctypes.c_int(rotary_dim), ctypes.c_int(1 if write_cache else 0), _stream()),
+        ctypes.c_float(eps), _pointer(cos), _pointer(sin), ctypes.c_int(rotary_dim), ctypes.c_int(1 if write_cache else 0),
+        ctypes.c_int(1 if cluster_merge else 0), _stream()),
         "attention_decode", launches)
 
 

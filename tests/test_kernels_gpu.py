@@ -375,10 +375,12 @@ def test_decode_attention_splits_and_groups(dtype, n_heads, n_kv_heads, head_dim
     wanted = torch.empty(5, n_heads * head_dim, dtype=dtype)
     plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
                                     n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
-    for splits in (1, 2, 5, 16):
-        found = torch.full_like(queries, float("nan"))
-        kernels.attention_decode(queries, keys, values, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window, splits)
-        close(found, wanted, dtype)
+    for splits in (1, 2, 5, 8, 16):
+        for cluster_merge in (True, False):   # up to 8 splits meet in a cluster's shared memory, or like more of them in global memory
+            found = torch.full_like(queries, float("nan"))
+            kernels.attention_decode(queries, keys, values, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window, splits,
+                                     cluster_merge=cluster_merge)
+            close(found, wanted, dtype)
 
 
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim,rotary_dim,with_norm,window", [
