@@ -293,6 +293,10 @@ __device__ __forceinline__ void prepare_head(const bf16* __restrict__ source, co
     for (int e = rotary_dim + lane; e < D; e += 32) target[e] = __float2bfloat16_rn(normalized(e));
 }
 
+#ifndef TAU_DECODE_CLUSTER
+#define TAU_DECODE_CLUSTER 16
+#endif
+constexpr int kClusterSplits = TAU_DECODE_CLUSTER;   // the most splits that merge inside a thread-block cluster (above 8: not portable)
 #ifndef TAU_DECODE_MIN_BLOCKS
 #define TAU_DECODE_MIN_BLOCKS 4
 #endif
@@ -540,9 +544,9 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
             const int h = index / D, c = index % D;
             const unsigned o_address = static_cast<unsigned>(__cvta_generic_to_shared(&merge_o[0][h][c]));
             const unsigned ml_address = static_cast<unsigned>(__cvta_generic_to_shared(&block_ml[h][0]));
-            float split_max[8], split_sum[8], split_o[8];
+            float split_max[kClusterSplits], split_sum[kClusterSplits], split_o[kClusterSplits];
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {
+            for (int s = 0; s < kClusterSplits; ++s) {
                 split_max[s] = -INFINITY;
                 split_sum[s] = 0.0f;
                 split_o[s] = 0.0f;
@@ -557,10 +561,10 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
             }
             float total_max = -INFINITY;
 #pragma unroll
-            for (int s = 0; s < 8; ++s) total_max = fmaxf(total_max, split_max[s]);
+            for (int s = 0; s < kClusterSplits; ++s) total_max = fmaxf(total_max, split_max[s]);
             float o = 0.0f, sum = 0.0f;
 #pragma unroll
-            for (int s = 0; s < 8; ++s) {
+            for (int s = 0; s < kClusterSplits; ++s) {
                 const float factor = exp2f(split_max[s] - total_max);   // 0 for an empty split, whose context is not used
                 if (factor > 0.0f) {
                     o += split_o[s] * factor;
@@ -687,8 +691,21 @@ TAU_EXPORT int tau_attention_decode(const void* queries, void* keys, void* value
     // Launched after the previous kernel has finished, not beside it: blocks that start on SMs which still hold the
     // blocks of the projection before them (100 KB of shared memory each) ran the whole kernel a half slower at batch 64
     // (138 us against 92 us per layer at 2,048 tokens of context), and at batch 8 starting early gained nothing.
-    // Up to 8 splits form a thread-block cluster and merge through shared memory; more meet in global memory by tickets.
-    const bool clustered = splits > 1 && splits <= 8 && cluster_merge != 0;
+    // Up to 16 splits form a thread-block cluster (above 8: a cluster size that is not portable, allowed on this part) and
+    // merge through shared memory; more meet in global memory by tickets.
+    const bool clustered = splits > 1 && splits <= kClusterSplits && cluster_merge != 0;
+    if (clustered && splits > 8) {
+        static bool allowed[4] = {false, false, false, false};
+        const int which = gh == 1 ? 0 : gh == 2 ? 1 : gh == 4 ? 2 : 3;
+        if (!allowed[which]) {
+            cudaError_t status = gh == 1   ? cudaFuncSetAttribute(decode_partial_mma_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
+                                 : gh == 2 ? cudaFuncSetAttribute(decode_partial_mma_kernel<2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
+                                 : gh == 4 ? cudaFuncSetAttribute(decode_partial_mma_kernel<4>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)
+                                           : cudaFuncSetAttribute(decode_partial_mma_kernel<8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (status != cudaSuccess) return static_cast<int>(status);
+            allowed[which] = true;
+        }
+    }
 #define TAU_LAUNCH(GH) do {                                                                                                        \
     if (clustered)                                                                                                                  \
         tau_launch_clusters_as(false, splits, decode_partial_mma_kernel<GH>, grid, dim3(kWarps * 32), 0, s, static_cast<const bf16*>(queries),       \

@@ -335,15 +335,20 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Four blocks of the
     decode kernel fit an SM, so the aim is the largest number of splits whose blocks are all resident at once
     (one wave: a second, partly filled wave costs more than the extra parallelism gives), each split at least 64
-    positions long.  Up to 8 splits merge inside a thread-block cluster, through shared memory, which saves 2 to 5 us
-    against the meeting in global memory; so up to 4,096 positions no more than 8 are used (one sequence of 2,049
-    positions: 11.4 us with 8 splits in a cluster, 12.0 us with 16, 13.8 us with 32), beyond that up to 32 (one sequence
-    of 32,001 positions: 39.8 us with 32, 54.4 us with 16).  The length is rounded up to a power of two first, so that
-    a captured graph (whose key holds this number) serves a whole range of lengths.
+    positions long.  Up to 16 splits merge inside a thread-block cluster, through shared memory, which saves 2 to 5 us
+    against the meeting in global memory (one sequence of 2,049 positions: 9.3 us with 16 splits in a cluster, 12.0 us
+    with 16 that meet in global memory; 8 sequences: 17.8 against 20.4 us with 8 splits).  Clusters of more than 8 blocks
+    are placed badly once they fill more than half of the SMs' places (4 sequences, 16 splits: 19.5 us against 14.1 us
+    with 8), so then 8 are used.  Beyond 8,192 positions up to 32 splits meet in global memory (one sequence of 32,001
+    positions: 40.4 us with 32, 54.9 us with 16 in a cluster).  The length is rounded up to a power of two first, so
+    that a captured graph (whose key holds this number) serves a whole range of lengths.
     """
     bucket = 1 << max(0, (max_len - 1).bit_length())
-    wanted = max(1, 592 // max(1, n_seqs * kv_blocks))
-    return max(1, min(wanted, bucket // 64, 8 if bucket <= 4096 else 32))
+    blocks = max(1, n_seqs * kv_blocks)
+    splits = max(1, min(592 // blocks, bucket // 64, 16 if bucket <= 8192 else 32))
+    if 8 < splits <= 16 and blocks * splits > 296:
+        splits = 8
+    return splits
 
 
 _decode_scratch = {}
@@ -357,7 +362,7 @@ def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: in
     `prepare` (bfloat16 only) is `(projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache)`: the kernel
     then takes queries, the newest key and the newest value from the stacked projection itself (per-head norm,
     rotation, cache write), `queries` may be None, and no prepare kernel is needed before it.
-    `cluster_merge` (bfloat16): up to 8 splits are one thread-block cluster and merge through shared memory; False makes
+    `cluster_merge` (bfloat16): up to 16 splits are one thread-block cluster and merge through shared memory; False makes
     them meet in global memory like larger numbers of splits.
     """
     _on_device(queries, keys, values, out, seq_len, page_rows)

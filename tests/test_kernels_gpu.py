@@ -375,8 +375,8 @@ def test_decode_attention_splits_and_groups(dtype, n_heads, n_kv_heads, head_dim
     wanted = torch.empty(5, n_heads * head_dim, dtype=dtype)
     plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
                                     n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window)
-    for splits in (1, 2, 5, 8, 16):
-        for cluster_merge in (True, False):   # up to 8 splits meet in a cluster's shared memory, or like more of them in global memory
+    for splits in (1, 2, 5, 8, 13, 16, 24):
+        for cluster_merge in (True, False):   # up to 16 splits meet in a cluster's shared memory, or like more of them in global memory
             found = torch.full_like(queries, float("nan"))
             kernels.attention_decode(queries, keys, values, found, seq_len, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, window, splits,
                                      cluster_merge=cluster_merge)
