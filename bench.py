@@ -105,6 +105,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers of the same sizes (named in the record)")
     parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=PROMPT_TOKENS, help="prompt length in tokens (the headline run uses 2,048)")
+    parser.add_argument("--prefill-chunk", type=int, default=0, help="prompts enter the cache in chunks of this many tokens (0: whole)")
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     parser.add_argument("--sections", default="prefill,decode,points,e2e", help="which measurements to run (for profiling a part alone)")
     args = parser.parse_args()
@@ -118,6 +120,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    prompt_tokens = args.context
+    slots_per_sequence = max(SLOTS_PER_SEQUENCE, (prompt_tokens + 1024 + 63) // 64 * 64)
+    chunk = args.prefill_chunk if args.prefill_chunk > 0 else prompt_tokens
 
     import numpy as np
     import torch
@@ -135,10 +140,10 @@ def main() -> int:
     vocab = config["vocab_size"]
 
     def prompts(count):
-        return [rng.integers(0, vocab, size=PROMPT_TOKENS).tolist() for _ in range(count)]
+        return [rng.integers(0, vocab, size=prompt_tokens).tolist() for _ in range(count)]
 
     def fresh_engine(batch):
-        return Engine(model, max_tokens=batch * SLOTS_PER_SEQUENCE, max_sequence_tokens=SLOTS_PER_SEQUENCE)
+        return Engine(model, max_tokens=batch * slots_per_sequence, max_sequence_tokens=slots_per_sequence)
 
     def timed(function):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -159,7 +164,9 @@ def main() -> int:
 
     def one_prefill():
         slot = engine.open_sequence()
-        engine.step([StepEntry(slot, prompt, [PROMPT_TOKENS - 1])])
+        for start in range(0, prompt_tokens, chunk):
+            piece = prompt[start : start + chunk]
+            engine.step([StepEntry(slot, piece, [len(piece) - 1] if start + chunk >= prompt_tokens else [])])
         engine.close_sequence(slot)
 
     prefill = None
@@ -167,18 +174,19 @@ def main() -> int:
         for _ in range(3):
             one_prefill()
         prefill_ms = min(timed(one_prefill) for _ in range(3))
-        flops = prefill_flops(config, args.layers, PROMPT_TOKENS)
-        prefill = {"value": round(PROMPT_TOKENS / prefill_ms * 1e3, 1), "tokens": PROMPT_TOKENS, "ms": round(prefill_ms, 3),
+        flops = prefill_flops(config, args.layers, prompt_tokens)
+        prefill = {"value": round(prompt_tokens / prefill_ms * 1e3, 1), "tokens": prompt_tokens, "ms": round(prefill_ms, 3),
                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "of": peaks["source"]}
     del engine
 
     # ---- decode -----------------------------------------------------------------------------
     def decode_run(batch, steps, warmup, sample_clocks=False):
-        """Device time of `steps` decode steps of `batch` sequences that hold 2,048-token prompts."""
+        """Device time of `steps` decode steps of `batch` sequences that hold prompts of the chosen length."""
         engine = fresh_engine(batch)
         slots = [engine.open_sequence() for _ in range(batch)]
         for slot, tokens in zip(slots, prompts(batch)):      # prompts one by one: bounded activations
-            engine.step([StepEntry(slot, tokens, [])])
+            for start in range(0, prompt_tokens, chunk):
+                engine.step([StepEntry(slot, tokens[start : start + chunk], [])])
         feed = rng.integers(0, vocab, size=(warmup + steps, batch)).tolist()
         sampler = tau_rs_b200.Sampler()
         chosen = torch.empty((2, batch), dtype=torch.int32, device="cuda:0")
@@ -226,21 +234,21 @@ def main() -> int:
     if "e2e" in sections:
         engine = fresh_engine(args.batch)
         batch_prompts = prompts(args.batch)
-        tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.warmup + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
-        output = tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.steps + 1, stop_tokens=(), prefill_chunk_tokens=PROMPT_TOKENS)
+        tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.warmup + 1, stop_tokens=(), prefill_chunk_tokens=chunk)
+        output = tau_rs_b200.generate(engine, batch_prompts, max_new_tokens=args.steps + 1, stop_tokens=(), prefill_chunk_tokens=chunk)
         e2e = {"value": round(output.metrics.decode_tokens_per_second, 1), "unit": "tok/s",
                "h2d_bytes_per_step": layout_ints * 4, "d2h_bytes_per_step": 2 * args.batch * 4,
                "steps": output.metrics.decode_steps}
 
     record = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if (args.batch, prompt_tokens) == (8, PROMPT_TOKENS) else f"decode tok/s at batch {args.batch}, {prompt_tokens:,}-token prompts (Qwen3-8B bf16)", "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)", "impl": "ours",
         "config": {
             "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": config["hidden_size"],
             "heads": config["num_attention_heads"], "kv_heads": config["num_key_value_heads"], "head_dim": config["head_dim"],
-            "intermediate": config["intermediate_size"], "vocab": vocab, "global_batch": args.batch, "seq_len": PROMPT_TOKENS,
-            "cache_slots_per_seq": SLOTS_PER_SEQUENCE, "rope_theta": config["rope_theta"], "rms_norm_eps": config["rms_norm_eps"],
+            "intermediate": config["intermediate_size"], "vocab": vocab, "global_batch": args.batch, "seq_len": prompt_tokens,
+            "cache_slots_per_seq": slots_per_sequence, "rope_theta": config["rope_theta"], "rms_norm_eps": config["rms_norm_eps"],
             "tied": False, "parallelism": "single GPU", "l2": "inputs (15 GB of weights) exceed L2; no flush",
             "weight_bytes": weight_bytes, "kv_bytes_per_step": live_bytes,
         },
