@@ -18,6 +18,13 @@ its own sequences to the device with its other metadata, so the device never hol
 of a sequence that has ended.  A `state` group has `[cache layers, slots, *shape]`
 and is zeroed for a slot when a sequence takes it.  Pages are not cleared: a position is
 written before anything reads it, and nothing reads beyond a sequence's length.
+
+A group whose need has a `window` gives a sequence's pages back as they fall out of the
+window: the next query, at position `length`, sees keys from `length - window + 1` on, so
+pages that lie wholly before that are returned when the length is published and their
+table entries are cleared.  Work already put on the stream may still read them; whoever
+takes them next writes them in work that is put on the stream later.  Such a sequence
+holds about `window / 64 + 2` pages however long it grows.
 """
 from __future__ import annotations
 
@@ -58,7 +65,11 @@ class _KVGroup:
         self.values = torch.empty(shape, dtype=dtype, device=device)
         self.pool = FreeList(pages, "cache page")
         self.table = np.zeros((slots, pages_per_sequence), dtype=np.int32)
-        self.held: Dict[int, List[int]] = {}
+        self.held: Dict[int, List[int]] = {}          # the pages a sequence holds, oldest first
+        self.released: Dict[int, int] = {}            # how many older pages it has given back already (a window's doing)
+
+    def tokens_read(self, length: int) -> int:
+        return min(length, self.need.window) if self.need.window else length
 
     def bytes_per_token(self) -> int:
         return 2 * self.layers * self.need.n_kv_heads * self.need.head_dim * self.keys.element_size()
@@ -83,7 +94,10 @@ class SequenceCache:
             raise ValueError("the cache must hold at least one token")
         self.device, self.dtype = device, dtype
         self.n_pages = pages_for(max_tokens)
-        self.pages_per_sequence = min(self.n_pages, pages_for(max_sequence_tokens))
+        # A sequence cannot hold more pages than there are, unless every kv group lets old pages go (a window).
+        kv_needs = [need for need, _ in groups.values() if need.kind == "kv"]
+        bounded = bool(kv_needs) and all(need.window for need in kv_needs)
+        self.pages_per_sequence = pages_for(max_sequence_tokens) if bounded else min(self.n_pages, pages_for(max_sequence_tokens))
         self.max_sequence_tokens = min(max_sequence_tokens, self.pages_per_sequence * PAGE_TOKENS)
         self.n_slots = min(self.n_pages, max_slots) if max_slots else self.n_pages
         self.slots = FreeList(self.n_slots, "sequence slot")
@@ -105,6 +119,7 @@ class SequenceCache:
         self.lengths[slot] = 0
         for group in self.kv.values():
             group.held[slot] = []
+            group.released[slot] = 0
         for group in self.states.values():
             group.state[:, slot].zero_()
         return slot
@@ -114,6 +129,7 @@ class SequenceCache:
         self._require_open(slot)
         for group in self.kv.values():
             group.pool.give_back(group.held.pop(slot))
+            del group.released[slot]
         del self.lengths[slot]
         self.slots.give_back([slot])
 
@@ -124,8 +140,8 @@ class SequenceCache:
     def pages_needed(self, slot: int, new_length: int) -> int:
         """Pages that `reserve(slot, new_length)` would take from each kv group."""
         self._require_open(slot)
-        held = max((len(group.held[slot]) for group in self.kv.values()), default=0)
-        return max(0, pages_for(new_length) - held) if self.kv else 0
+        wanted = pages_for(new_length)
+        return max((max(0, wanted - group.released[slot] - len(group.held[slot])) for group in self.kv.values()), default=0)
 
     def reserve(self, slot: int, new_length: int) -> None:
         """Makes room for the sequence to grow to `new_length` positions."""
@@ -134,11 +150,11 @@ class SequenceCache:
             raise CacheFull(f"a sequence of {new_length} tokens exceeds the limit of {self.max_sequence_tokens}")
         for group in self.kv.values():
             held = group.held[slot]
-            extra = pages_for(new_length) - len(held)
+            begin = group.released[slot] + len(held)
+            extra = pages_for(new_length) - begin
             if extra <= 0:
                 continue
             taken = group.pool.take(extra)
-            begin = len(held)
             held.extend(taken)
             group.table[slot, begin : begin + extra] = taken
 
@@ -147,6 +163,18 @@ class SequenceCache:
         if new_length < self.lengths[slot]:
             raise ValueError("a sequence cannot shrink")
         self.lengths[slot] = new_length
+        for group in self.kv.values():
+            if not group.need.window:
+                continue
+            # The next query sits at position `new_length` and sees keys from `new_length - window + 1` on.
+            keep_from = max(0, new_length - group.need.window + 1) // PAGE_TOKENS
+            gone = keep_from - group.released[slot]
+            if gone > 0:
+                held = group.held[slot]
+                group.pool.give_back(held[:gone])
+                del held[:gone]
+                group.table[slot, group.released[slot] : keep_from] = 0
+                group.released[slot] = keep_from
 
     def page_rows(self, group: str, slots, pages: int) -> np.ndarray:
         """Page numbers `[len(slots), pages]` of the given sequences (host memory)."""
@@ -172,7 +200,7 @@ class SequenceCache:
 
     def live_bytes(self) -> int:
         """Bytes of keys and values that a step over all live sequences reads."""
-        return sum(self.lengths.values()) * self.bytes_per_token()
+        return sum(group.tokens_read(length) * group.bytes_per_token() for length in self.lengths.values() for group in self.kv.values())
 
     def check(self) -> None:
         """No slot or page lost, held twice or shared between sequences."""
@@ -187,5 +215,9 @@ class SequenceCache:
             if len(held) != group.pool.in_use:
                 raise AssertionError("a cache page is in use but belongs to no sequence")
             for slot, pages in group.held.items():
-                if self.lengths[slot] > len(pages) * PAGE_TOKENS:
+                if self.lengths[slot] > (group.released[slot] + len(pages)) * PAGE_TOKENS:
                     raise AssertionError("a sequence is longer than the pages it holds")
+                if group.released[slot] and not group.need.window:
+                    raise AssertionError("a group without a window gave pages back early")
+                if group.need.window and group.released[slot] * PAGE_TOKENS > max(0, self.lengths[slot] - group.need.window + 1):
+                    raise AssertionError("a page inside the window was given back")

@@ -88,3 +88,59 @@ def run_batched(engine: Engine, requests: Sequence[Sequence[int]], prompt_length
 def relative_error(found: torch.Tensor, wanted: torch.Tensor) -> float:
     """Largest absolute difference over the largest absolute wanted value."""
     return float((found.double() - wanted.double()).abs().max() / wanted.double().abs().max())
+
+
+# ---- a toy architecture whose attention layers all have a window (so that their cache gives old pages back) ----------
+def window_spec(config):
+    from tau_rs_b200.config import AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleEntry, SwiGLUSpec
+
+    hidden = config["hidden_size"]
+    norm = NormSpec(width=hidden, eps=config["eps"])
+    position = PositionSpec(rotary_dim=16, theta=1000.0, max_positions=config["max_positions"])
+    first = AttentionSpec(hidden=hidden, n_heads=4, n_kv_heads=2, head_dim=16, bias=False, softmax_scale=0.25,
+                          qk_norm=NormSpec(width=16, eps=config["eps"]), position=position, window=config["window"])
+    second = AttentionSpec(hidden=hidden, n_heads=2, n_kv_heads=1, head_dim=32, bias=True, softmax_scale=32 ** -0.5, qk_norm=None,
+                           position=position, window=config["window"] // 2)
+    feed = SwiGLUSpec(hidden=hidden, intermediate=config["intermediate_size"])
+    blocks = (BlockSpec("toy.layers.0", first, feed, norm, norm), BlockSpec("toy.layers.1", second, feed, norm, norm))
+    schedule = (ScheduleEntry(layer=0, cache_group="wide", cache_layer=0), ScheduleEntry(layer=1, cache_group="narrow", cache_layer=0))
+    return ModelSpec(architecture="ToyWindowForCausalLM", vocab_size=config["vocab_size"], hidden=hidden, max_positions=config["max_positions"],
+                     embedding_name="toy.embed.weight", blocks=blocks, schedule=schedule, final_norm=norm,
+                     final_norm_name="toy.norm.weight", head_name="toy.head.weight", tie_head=True)
+
+
+WINDOW_CONFIG = {"architectures": ["ToyWindowForCausalLM"], "model_type": "toy_window", "hidden_size": 32, "intermediate_size": 48,
+                 "vocab_size": 53, "max_positions": 1024, "eps": 1e-5, "window": 70}
+
+
+def windowed_cache_matches_whole_prompt(folder, dtype, device, tolerance):
+    """A sequence of 600 tokens through an engine whose cache holds 4 pages (256 positions), in chunks and single tokens, against
+    the same tokens in one step through an engine with room for all of them: the pages that fell out of the windows were given
+    back and taken again, and nothing that a query may see was lost."""
+    import numpy as np
+
+    from tau_rs_b200 import Engine, StepEntry, load_model
+
+    model = load_model(folder, dtype, device)
+    tokens = np.random.default_rng(3).integers(0, WINDOW_CONFIG["vocab_size"], size=600).tolist()
+    roomy = Engine(model, 64 * 10)
+    slot = roomy.open_sequence()
+    wanted = roomy.step([StepEntry(slot, tokens, list(range(len(tokens))))]).cpu().clone()
+    roomy.close_sequence(slot)
+    tight = Engine(model, 64 * 4)
+    assert tight.max_sequence_tokens == WINDOW_CONFIG["max_positions"]
+    slot = tight.open_sequence()
+    found, position = [], 0
+    for count in [50, 1, 1, 64, 30, 1, 1, 1, 50, 50, 50, 64, 1, 50, 50, 50, 36] + [1] * 50:
+        piece = tokens[position : position + count]
+        found.append(tight.step([StepEntry(slot, piece, list(range(len(piece))))]).cpu().clone())
+        position += len(piece)
+        tight.cache.check()
+        assert len(tight.cache.kv["wide"].held[slot]) <= 3 and len(tight.cache.kv["narrow"].held[slot]) <= 3
+    assert position == 600
+    tight.close_sequence(slot)
+    tight.cache.check()
+    import torch
+
+    found = torch.cat(found)
+    assert relative_error(found, wanted) < tolerance

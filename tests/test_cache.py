@@ -112,3 +112,52 @@ def test_random_traffic_keeps_every_invariant():
         cache.close(slot)
     cache.check()
     assert cache.free_tokens() == 64 * 12
+
+
+def test_a_window_gives_pages_back_as_they_fall_out_of_it():
+    """A group with a window of 100 positions: a sequence grows to 1,000 positions in a cache of 5 pages, holds at most 3 pages
+    at a time, and its table names no page that it no longer holds."""
+    need = CacheNeed("kv", n_kv_heads=1, head_dim=16, window=100)
+    cache = SequenceCache({"w": (need, 2)}, max_tokens=64 * 5, max_sequence_tokens=1024, dtype=torch.float32, device=torch.device("cpu"))
+    assert cache.pages_per_sequence == 16 and cache.max_sequence_tokens == 1024      # not bounded by the 5 pages there are
+    slot, other = cache.open(), cache.open()
+    cache.reserve(other, 64)
+    cache.advance(other, 64)                  # a neighbour that keeps one page throughout
+    length = 0
+    for step in (70, 1, 1, 50, 64, 1, 100, 13):
+        for _ in range(3):
+            if length + step > 1000:
+                break
+            assert cache.pages_needed(slot, length + step) <= cache.free_tokens() // 64
+            cache.reserve(slot, length + step)
+            length += step
+            cache.advance(slot, length)
+            cache.check()
+            group = cache.kv["w"]
+            first_needed = max(0, length - 100 + 1) // 64
+            assert group.released[slot] == first_needed
+            assert len(group.held[slot]) == -(-length // 64) - first_needed <= 3
+            row = cache.page_rows("w", [slot], cache.pages_per_sequence)[0]
+            assert list(row[first_needed : first_needed + len(group.held[slot])]) == group.held[slot]
+            assert not row[:first_needed].any()
+    cache.close(slot)
+    cache.close(other)
+    cache.check()
+    assert cache.free_tokens() == 64 * 5
+
+
+def test_groups_with_and_without_a_window_side_by_side():
+    """The group without a window keeps every page (and bounds the sequence by the pages there are); the other lets go."""
+    groups = {"all": (CacheNeed("kv", n_kv_heads=1, head_dim=16), 1), "w": (CacheNeed("kv", n_kv_heads=2, head_dim=32, window=64), 1)}
+    cache = SequenceCache(groups, max_tokens=64 * 6, max_sequence_tokens=4096, dtype=torch.float32, device=torch.device("cpu"))
+    assert cache.pages_per_sequence == 6
+    slot = cache.open()
+    cache.reserve(slot, 300)
+    cache.advance(slot, 300)
+    assert len(cache.kv["all"].held[slot]) == 5 and cache.kv["all"].released[slot] == 0
+    assert len(cache.kv["w"].held[slot]) == 2 and cache.kv["w"].released[slot] == 3
+    assert cache.free_tokens() == 64          # the fuller pool decides
+    assert cache.live_bytes() == 300 * cache.kv["all"].bytes_per_token() + 64 * cache.kv["w"].bytes_per_token()
+    cache.check()
+    cache.close(slot)
+    cache.check()

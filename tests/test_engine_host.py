@@ -135,3 +135,17 @@ def test_step_takes_token_ids_from_the_device_or_refuses_them(cpu_kernels, folde
         assert engine.sequence_length(slot) == length      # refused before anything changed
     engine.close_sequence(slot)
     engine.cache.check()
+
+
+def test_windowed_layers_give_pages_back_and_lose_nothing(cpu_kernels, tmp_path):
+    from helpers import WINDOW_CONFIG, window_spec, windowed_cache_matches_whole_prompt
+    from tau_rs_b200 import write_random_model
+    from tau_rs_b200.config import register_architecture, unregister_architecture
+
+    register_architecture("ToyWindowForCausalLM", "toy_window", lambda raw: raw, window_spec)
+    try:
+        folder = str(tmp_path / "window")
+        write_random_model(folder, WINDOW_CONFIG, seed=9, norm_jitter=0.1, storage="float32")
+        windowed_cache_matches_whole_prompt(folder, "float32", torch.device("cpu"), 1e-4)
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")

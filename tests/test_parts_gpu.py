@@ -449,3 +449,17 @@ def test_a_toy_routed_feed_forward_and_another_position_encoding(routed_architec
     # The slowdown is felt: the same weights with the usual tables give other logits.
     usual = plain_model.rope_tables(16, 500.0, 160)
     assert not torch.allclose(torch.stack(slowed_tables(spec.blocks[0].mixer.position)), torch.stack(usual))
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 2e-2)])
+def test_windowed_layers_give_pages_back_and_lose_nothing(dtype, tolerance, tmp_path):
+    """Every attention layer has a window: a 600-token sequence runs in a cache of 256 positions, pages given back and taken again."""
+    from helpers import WINDOW_CONFIG, window_spec, windowed_cache_matches_whole_prompt
+
+    register_architecture("ToyWindowForCausalLM", "toy_window", lambda raw: raw, window_spec)
+    try:
+        folder = str(tmp_path / "window")
+        write_random_model(folder, WINDOW_CONFIG, seed=9, norm_jitter=0.1, storage=dtype)
+        windowed_cache_matches_whole_prompt(folder, dtype, DEVICE, tolerance)
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")
