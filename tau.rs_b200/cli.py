@@ -40,7 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
     execution.add_argument("--cache-tokens", type=int, default=None, metavar="N", help="Tokens the cache holds (each live request rounded up to 64). [default: what the requests need]")
     request = parser.add_argument_group("Request options")
     request.add_argument("--prompt-ids", action="append", default=[], metavar="1,2,3", help="Token ids of one prompt; may be given several times.")
-    request.add_argument("--prompt-file", metavar="PATH", help="JSON file: a list of prompts, each a list of token ids.")
+    request.add_argument("--prompt-file", metavar="PATH", help="File of prompts: a JSON list of lists of token ids, or one prompt a line (ids parted by commas or spaces).")
     request.add_argument("--max-tokens", type=int, default=None, metavar="N", help="Most tokens to generate per request. [default: generation settings of the folder, else 16]")
     request.add_argument("--temperature", type=float, default=0.0, help="0: greedy. [default: 0]")
     request.add_argument("--stop-ids", default=None, metavar="1,2", help="Stop token ids. [default: eos_token_id of the folder]")
@@ -51,7 +51,22 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def _ids(text: str) -> List[int]:
-    return [int(part) for part in text.replace(" ", "").split(",") if part]
+    return [int(part) for part in text.replace(",", " ").split()]
+
+
+def read_prompt_file(path: str) -> List[List[int]]:
+    """A JSON list of prompts (each a list of token ids), or one prompt a line with ids parted by commas or spaces."""
+    with open(path) as handle:
+        text = handle.read()
+    try:
+        if text.lstrip().startswith("["):
+            prompts = json.loads(text)
+            if isinstance(prompts, list) and all(isinstance(prompt, list) and prompt and all(isinstance(token, int) and not isinstance(token, bool) for token in prompt) for prompt in prompts):
+                return prompts
+            raise ValueError("not a list of non-empty lists of integers")
+        return [_ids(line) for line in text.splitlines() if line.strip()]
+    except ValueError as error:
+        raise SystemExit(f"--prompt-file {path}: expected a JSON list of lists of token ids, or one prompt of ids a line ({error})")
 
 
 class _Tracer:
@@ -94,8 +109,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(f"wrote {args.model} (seed {args.seed}, {storage})", file=sys.stderr)
     prompts = [_ids(text) for text in args.prompt_ids]
     if args.prompt_file:
-        with open(args.prompt_file) as handle:
-            prompts += json.load(handle)
+        prompts += read_prompt_file(args.prompt_file)
     if not prompts:
         if args.random_weights:
             return 0

@@ -228,3 +228,19 @@ def test_one_step_ahead_equals_step_by_step_on_random_requests():
         assert [(r.tokens, r.finish_reason, r.prompt_tokens) for r in ahead] == [(r.tokens, r.finish_reason, r.prompt_tokens) for r in plain], trial
         assert not backend.open and sorted(backend.closed) == sorted(backend.opened)
         assert metrics.generated_tokens == sum(len(r.tokens) for r in ahead)
+
+
+def test_prompt_file_takes_json_or_lines(tmp_path):
+    from tau_rs_b200.cli import read_prompt_file
+
+    as_json = tmp_path / "prompts.json"
+    as_json.write_text("[[5, 6, 7], [8, 9]]\n")
+    assert read_prompt_file(str(as_json)) == [[5, 6, 7], [8, 9]]
+    as_lines = tmp_path / "prompts.txt"
+    as_lines.write_text("5 6 7\n\n8,9\n 10, 11 \n")
+    assert read_prompt_file(str(as_lines)) == [[5, 6, 7], [8, 9], [10, 11]]
+    for bad in ("[[1, 2], []]", "[1, 2]", "[[1.5]]", "1 two 3\n", "[[1, 2]"):
+        wrong = tmp_path / "wrong"
+        wrong.write_text(bad)
+        with pytest.raises(SystemExit, match="prompt-file"):
+            read_prompt_file(str(wrong))
