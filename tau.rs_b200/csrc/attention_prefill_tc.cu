@@ -549,6 +549,7 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
         return cudaErrorInvalidValue;
     CUtensorMap q_map, k_map, v_map;
     const long long cache_rows = n_pages * n_kv_heads * BN;
+    if (cache_rows > 0x7fffffffLL) return cudaErrorInvalidValue;   // a tile's row is a 32-bit coordinate of the copy
     if (!make_map(&q_map, queries, n_tokens, static_cast<long long>(n_heads) * D, BM) || !make_map(&k_map, keys, cache_rows, D, BN) ||
         !make_map(&v_map, values, cache_rows, D, BN))
         return cudaErrorInvalidValue;

@@ -496,7 +496,9 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
         splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
         return attention_decode(queries, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits)
     if queries.dtype == torch.bfloat16:
-        prefill = attention_prefill_tc if head_dim in (64, 128) else attention_prefill
+        # The tensor-memory kernel addresses the cache by 32-bit rows (pages x kv heads x 64); a larger cache goes to the other kernel.
+        rows_fit = keys.shape[0] * n_kv_heads * PAGE_TOKENS <= 0x7FFFFFFF
+        prefill = attention_prefill_tc if head_dim in (64, 128) and rows_fit else attention_prefill
         return prefill(queries, keys, values, out, step.cu_seqlens, step.seq_start, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
 
