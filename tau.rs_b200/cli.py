@@ -5,6 +5,7 @@ Options that the reference has keep its names and meanings: `-m/--model PATH`,
 is refused as the reference refuses bfloat16 there), `--dtype auto|f32|bf16` (auto: bf16 if
 the folder declares it), `--cuda-graph none|full`, `--prefill-chunk-size N`, `--metrics`
 (an `inference_metrics {...}` line on stderr, crates/metrics/src/serving.rs:35-54),
+`--vram-metrics` (an `inference_vram_metrics {...}` line on stderr, crates/metrics/src/memory.rs:119-138),
 `--tracing` (an `inference_trace {...}` line on stdout with prompt ids, generated ids and
 per-step logit checksums, crates/metrics/src/trace.rs:22-52,88-106; logits then go to the
 host and the host selector of crates/engine/src/generation.rs:81-95 is not needed because
@@ -47,6 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     logging = parser.add_argument_group("Logging options")
     logging.add_argument("--metrics", action="store_true", help="Log throughput to stderr. [default: off]")
     logging.add_argument("--tracing", action="store_true", help="Log numerical traces (token ids, logit checksums) to stdout. [default: off]")
+    logging.add_argument("--vram-metrics", action="store_true", help="Sample process VRAM; log peak to stderr. [default: off] Independent of --metrics and --tracing.")
     return parser
 
 
@@ -131,12 +133,24 @@ def main(argv: Optional[List[str]] = None) -> int:
         cache_tokens = max(64, sum(needs[: args.max_batch]))
     engine = Engine(model, cache_tokens)
     engine.use_graphs = engine.use_graphs and args.cuda_graph == "full"
-    select = Sampler(SamplingParams(args.temperature, args.seed)).select
+    select = Sampler(SamplingParams(args.temperature, args.seed))   # the object, not its method: the loop then decodes one step ahead
     tracer = _Tracer(select) if args.tracing else None
     metrics = GenerationMetrics()
+    memory = None
+    if args.vram_metrics:
+        from . import vram
+
+        memory = vram.device_sampler().start()
     started = time.perf_counter()
-    results = generate_tokens(engine, prompts, limit, tracer or select, stop, args.max_batch, args.prefill_chunk_size, metrics)
+    try:
+        results = generate_tokens(engine, prompts, limit, tracer or select, stop, args.max_batch, args.prefill_chunk_size, metrics)
+    except Exception as error:
+        if memory is not None:
+            vram.report(memory.finish(), args.model, error=str(error))
+        raise
     elapsed = time.perf_counter() - started
+    if memory is not None:
+        vram.report(memory.finish(), args.model)
     for index, result in enumerate(results):
         print(json.dumps({"request": index, "prompt_tokens": result.prompt_tokens, "completion_tokens": len(result.tokens),
                           "tokens": result.tokens, "finish_reason": result.finish_reason}))

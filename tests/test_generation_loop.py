@@ -244,3 +244,42 @@ def test_prompt_file_takes_json_or_lines(tmp_path):
         wrong.write_text(bad)
         with pytest.raises(SystemExit, match="prompt-file"):
             read_prompt_file(str(wrong))
+
+
+def test_vram_sampler_keeps_start_peak_end_and_a_failed_sample():
+    """The record of `--vram-metrics`: crates/metrics/src/memory.rs:47-64 (peak over the samples, delta against the start,
+    an error kept even if later samples succeed)."""
+    import io
+    import json
+    import time
+
+    from tau_rs_b200 import vram
+
+    values = iter([100, 180, RuntimeError("query failed"), 260, 150, 120])
+    taken = []
+
+    def sample():
+        value = next(values, 120)
+        taken.append(value)
+        if isinstance(value, Exception):
+            raise value
+        return value
+
+    sampler = vram.VramSampler(sample, "process_on_device", "GPU-0000", interval_ms=5).start()
+    while len(taken) < 5:
+        time.sleep(0.005)
+    snapshot = sampler.finish()
+    assert snapshot["vram_start_bytes"] == 100 and snapshot["vram_peak_sampled_bytes"] == 260
+    assert snapshot["vram_end_bytes"] in (150, 120) and snapshot["vram_peak_delta_bytes"] == 160
+    assert snapshot["vram_error"] == "query failed" and snapshot["vram_samples"] == len(taken) - 1
+    assert snapshot["vram_sample_interval_ms"] == 5 and snapshot["vram_scope"] == "process_on_device"
+    out = io.StringIO()
+    line = vram.report(snapshot, "folder", request_id=3, stream=out)
+    assert line.startswith("inference_vram_metrics ") and out.getvalue().strip() == line
+    record = json.loads(line.split(" ", 1)[1])
+    assert record["request_id"] == 3 and record["model"] == "folder" and record["status"] == "ok" and record["error"] is None
+    assert record["vram_peak_sampled_bytes"] == 260 and record["vram_device_uuid"] == "GPU-0000"
+    failed = json.loads(vram.report(snapshot, "folder", error="out of pages", stream=out).split(" ", 1)[1])
+    assert failed["status"] == "error" and failed["error"] == "out of pages"
+    never = vram.VramSampler(lambda: (_ for _ in ()).throw(RuntimeError("no device")), "device", None, interval_ms=5).start().finish()
+    assert never["vram_start_bytes"] is None and never["vram_peak_delta_bytes"] is None and never["vram_error"] == "no device"
