@@ -3,7 +3,8 @@
 Options that the reference has keep its names and meanings: `-m/--model PATH`,
 `--device auto|gpu|cpu` (args.rs: auto is CUDA GPU 0; this library has no CPU path, so `cpu`
 is refused as the reference refuses bfloat16 there), `--dtype auto|f32|bf16` (auto: bf16 if
-the folder declares it), `--cuda-graph none|full`, `--prefill-chunk-size N`, `--metrics`
+the folder declares it), `--optimize-kernel true|false` (false: this library's plain kernels, as the
+reference's are Candle's), `--cuda-graph none|full`, `--prefill-chunk-size N`, `--metrics`
 (an `inference_metrics {...}` line on stderr, crates/metrics/src/serving.rs:35-54),
 `--vram-metrics` (an `inference_vram_metrics {...}` line on stderr, crates/metrics/src/memory.rs:119-138),
 `--tracing` (an `inference_trace {...}` line on stdout with prompt ids, generated ids and
@@ -35,6 +36,8 @@ def build_parser() -> argparse.ArgumentParser:
     model.add_argument("--seed", type=int, default=0, help="Seed of random weights and of temperature sampling. [default: 0]")
     model.add_argument("--norm-jitter", type=float, default=0.0, help="Random weights: norm weights are 1 + N(0, jitter). [default: 0]")
     execution = parser.add_argument_group("Execution options")
+    execution.add_argument("--optimize-kernel", default="true", choices=["true", "false"],
+                           help="Prefer optimized kernels. [default: true] false: the plain kernels that the others are checked against.")
     execution.add_argument("--cuda-graph", default="full", choices=["none", "full"], help="CUDA graph policy for decode steps. [default: full]")
     execution.add_argument("--prefill-chunk-size", type=int, default=8192, metavar="N", help="Most prompt tokens per prefill step, over the whole batch. [default: 8192]")
     execution.add_argument("--max-batch", type=int, default=64, metavar="N", help="Most requests that start together. [default: 64]")
@@ -123,6 +126,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .engine.step import Engine
     from .sampling.sampler import Sampler, SamplingParams
 
+    from .csrc import kernels
+
+    kernels.prefer_optimized(args.optimize_kernel == "true")
     model = load_model(args.model, args.dtype, args.device)
     settings: GenerationConfig = model.generation_config
     limit = args.max_tokens if args.max_tokens is not None else settings.max_new_tokens

@@ -251,9 +251,22 @@ def gemm_library(values, weight, bias, out) -> None:
 GATE_GROUP = 8   # rows of a gate (and of its up) that lie together in a weight prepared for `linear_gated`
 
 
+_prefer_optimized = True
+
+
+def prefer_optimized(enabled: bool) -> None:
+    """`--optimize-kernel true|false` (crates/server/src/args.rs: "Prefer optimized kernels ... false: use reference
+    kernels").  With `False` every product is the plain tiled kernel, every attention the one-warp-per-head kernel over
+    the pages, and nothing is fused: the slow kernels that the others are checked against, for telling a kernel's
+    fault from the engine's.  Set it before the model is built: a feed-forward decides then whether its gate and up
+    rows are interleaved for the gated product."""
+    global _prefer_optimized
+    _prefer_optimized = bool(enabled)
+
+
 def gated_fits(in_features: int, out_features: int, dtype) -> bool:
     """Whether `linear_gated` serves a gate/up pair of these sizes (else: `linear`, then `silu_mul`)."""
-    return dtype == torch.bfloat16 and in_features % 8 == 0 and out_features % GATE_GROUP == 0
+    return _prefer_optimized and dtype == torch.bfloat16 and in_features % 8 == 0 and out_features % GATE_GROUP == 0
 
 
 def linear_gated(values, weight, out) -> None:
@@ -267,7 +280,7 @@ def linear_gated(values, weight, out) -> None:
 
 def linear(values, weight, bias, out) -> None:
     """`out = values @ weight.T + bias` with the kernel that fits the dtype and the sizes."""
-    if values.dtype == torch.bfloat16:
+    if values.dtype == torch.bfloat16 and _prefer_optimized:
         if _skinny_fits(values, weight, out) and values.shape[0] <= SKINNY_BEST_ROWS:
             return gemm_skinny(values, weight, bias, out)
         if _tc_fits(values, weight, out):
@@ -427,7 +440,7 @@ def attention_decode_fused(projected, keys, values, out, step, page_rows, write_
                            rotary_dim: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int) -> bool:
     """Prepare and decode attention in one kernel, where that exists: every sequence brings one token and the dtype is
     bfloat16.  Returns False (and does nothing) otherwise; the caller then runs `attention_prepare` and `attention`."""
-    if not (step.all_single and projected.dtype == torch.bfloat16):
+    if not (step.all_single and projected.dtype == torch.bfloat16 and _prefer_optimized):
         return False
     splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
     attention_decode(None, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits,
@@ -492,6 +505,8 @@ def attention_prefill_tc_status(head_dim: int) -> int:
 def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
               window: int) -> None:
     """Causal attention of the step's tokens over their sequences' cache pages (which hold the step's own keys already)."""
+    if not _prefer_optimized:
+        return attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
     if step.all_single:
         splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
         return attention_decode(queries, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits)

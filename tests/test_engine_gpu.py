@@ -197,3 +197,34 @@ def test_same_request_twice_gives_the_same_tokens(folders):
     second = generate(engine, prompts, max_new_tokens=16, stop_tokens=())
     assert first[0].tokens == second[0].tokens
     engine.cache.check()
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "bfloat16"), ("B", "bfloat16"), ("C", "float32")])
+def test_plain_kernels_alone_give_the_same_logits(folders, which, dtype):
+    """`--optimize-kernel false`: products by the tiled kernel, attention by the kernel over the pages, nothing fused.
+    Whole prompts, the last tokens one by one, and an unequal batch, against the plain implementation and against the
+    fast kernels: a fault that one of the two shows alone lies in a kernel, one that both show in the engine."""
+    from tau_rs_b200.csrc import kernels
+
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    limit = tiny_configs.CONFIGS[which]["max_position_embeddings"]
+    (tokens,) = random_prompts(vocab, [min(limit, 120)], seed=41)
+    requests = random_prompts(vocab, [40, 23, 9], seed=42)
+    found = {}
+    try:
+        for optimized in (False, True):
+            kernels.prefer_optimized(optimized)
+            engine = engine_for(folders[(which, dtype)], dtype, "gpu", 1024)   # built under the setting: the feed-forward's weight layout follows it
+            assert engine.model.blocks[0].feed_forward.fused == (optimized and dtype == "bfloat16")
+            found[optimized] = (run_whole(engine, tokens), run_tail_stepwise(engine, tokens, 32), run_batched(engine, requests, [30, 3, 8]))
+            engine.cache.check()
+    finally:
+        kernels.prefer_optimized(True)
+    wanted = expected(folders, which, dtype, tokens)
+    for optimized in (False, True):
+        whole, tail, batched = found[optimized]
+        assert relative_error(whole, wanted) < TOLERANCE[dtype]
+        assert relative_error(tail, wanted[-32:]) < TOLERANCE[dtype]
+        for request, prompt_length, logits in zip(requests, [30, 3, 8], batched):
+            assert relative_error(logits, expected(folders, which, dtype, request)[prompt_length - 1 :]) < TOLERANCE[dtype]
+    assert relative_error(found[False][0], found[True][0]) < TOLERANCE[dtype]
