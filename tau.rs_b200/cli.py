@@ -4,7 +4,8 @@ Options that the reference has keep its names and meanings: `-m/--model PATH`,
 `--device auto|gpu|cpu` (args.rs: auto is CUDA GPU 0; this library has no CPU path, so `cpu`
 is refused as the reference refuses bfloat16 there), `--dtype auto|f32|bf16` (auto: bf16 if
 the folder declares it), `--optimize-kernel true|false` (false: this library's plain kernels, as the
-reference's are Candle's), `--cuda-graph none|full`, `--prefill-chunk-size N`, `--metrics`
+reference's are Candle's), `--cuda-graph none|full`, `--attention-block-size 32|64|128|256` (context tokens per block of decode attention; the
+reference's default is a fixed size, here the number of blocks follows the batch and the context unless it is given), `--prefill-chunk-size N`, `--metrics`
 (an `inference_metrics {...}` line on stderr, crates/metrics/src/serving.rs:35-54),
 `--vram-metrics` (an `inference_vram_metrics {...}` line on stderr, crates/metrics/src/memory.rs:119-138),
 `--tracing` (an `inference_trace {...}` line on stdout with prompt ids, generated ids and
@@ -39,6 +40,8 @@ def build_parser() -> argparse.ArgumentParser:
     execution.add_argument("--optimize-kernel", default="true", choices=["true", "false"],
                            help="Prefer optimized kernels. [default: true] false: the plain kernels that the others are checked against.")
     execution.add_argument("--cuda-graph", default="full", choices=["none", "full"], help="CUDA graph policy for decode steps. [default: full]")
+    execution.add_argument("--attention-block-size", type=int, default=None, choices=[32, 64, 128, 256], metavar="32|64|128|256",
+                           help="Context tokens per block of decode attention. [default: chosen from the batch and the context]")
     execution.add_argument("--prefill-chunk-size", type=int, default=8192, metavar="N", help="Most prompt tokens per prefill step, over the whole batch. [default: 8192]")
     execution.add_argument("--max-batch", type=int, default=64, metavar="N", help="Most requests that start together. [default: 64]")
     execution.add_argument("--cache-tokens", type=int, default=None, metavar="N", help="Tokens the cache holds (each live request rounded up to 64). [default: what the requests need]")
@@ -139,6 +142,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         cache_tokens = max(64, sum(needs[: args.max_batch]))
     engine = Engine(model, cache_tokens)
     engine.use_graphs = engine.use_graphs and args.cuda_graph == "full"
+    engine.attention_block_size = args.attention_block_size
     select = Sampler(SamplingParams(args.temperature, args.seed))   # the object, not its method: the loop then decodes one step ahead
     tracer = _Tracer(select) if args.tracing else None
     metrics = GenerationMetrics()

@@ -442,7 +442,7 @@ def attention_decode_fused(projected, keys, values, out, step, page_rows, write_
     bfloat16.  Returns False (and does nothing) otherwise; the caller then runs `attention_prepare` and `attention`."""
     if not (step.all_single and projected.dtype == torch.bfloat16 and _prefer_optimized):
         return False
-    splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
+    splits = min(step.decode_splits or decode_splits(step.n_seqs, step.max_len), 2 * head_dim)   # the kernel's limit on a given number
     attention_decode(None, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits,
                      prepare=(projected, q_weight, k_weight, eps, cos, sin, rotary_dim, write_cache))
     return True
@@ -508,7 +508,7 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
     if not _prefer_optimized:
         return attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
     if step.all_single:
-        splits = step.decode_splits or decode_splits(step.n_seqs, step.max_len)
+        splits = min(step.decode_splits or decode_splits(step.n_seqs, step.max_len), 2 * head_dim)
         return attention_decode(queries, keys, values, out, step.seq_len, page_rows, n_heads, n_kv_heads, head_dim, scale, window, splits)
     if queries.dtype == torch.bfloat16:
         # The tensor-memory kernel addresses the cache by 32-bit rows (pages x kv heads x 64); a larger cache goes to the other kernel.

@@ -62,7 +62,7 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
     bucket = (len(entries), max(0, (max_len - 1).bit_length()))
     splits = engine._split_choice.get(bucket)
     if splits is None:
-        splits = engine._split_choice[bucket] = engine.model.decode_splits(len(entries), max_len)
+        splits = engine._split_choice[bucket] = engine.decode_splits(len(entries), max_len)
     key = (len(entries), splits)
     state = engine._graphs.get(key)
     if state is None:

@@ -27,6 +27,9 @@ class StepError(ValueError):
     """The step's entries do not fit the sequences they name."""
 
 
+MAX_DECODE_SPLITS = 64   # decode attention merges at most this many blocks of a context (the kernel takes up to 2 * head_dim)
+
+
 class Engine:
     """A model, its cache and the step function over both."""
 
@@ -43,6 +46,16 @@ class Engine:
         self.last_step_ints = 0     # size of the last step's metadata (int32 words copied to the device)
         # A captured step runs more than once while it is captured; state that a mixer updates in place forbids that.
         self.use_graphs = self.device.type == "cuda" and not self.cache.states
+        # Context tokens per block of decode attention (`--attention-block-size`, crates/server/src/args.rs: "context tokens
+        # per prepared decode attention tile"); None: chosen from the batch and the context by `DecoderModel.decode_splits`.
+        self.attention_block_size: Optional[int] = None
+
+    def decode_splits(self, n_seqs: int, max_len: int) -> int:
+        """Blocks that the context of a decode step is cut into for attention."""
+        if self.attention_block_size:
+            bucket = 1 << max(0, (max_len - 1).bit_length())   # as the graphs are keyed: a power of two of positions
+            return max(1, min(-(-bucket // self.attention_block_size), MAX_DECODE_SPLITS))
+        return self.model.decode_splits(n_seqs, max_len)
 
     def ring(self, ints: int) -> PinnedRing:
         """The pinned staging ring, grown if a step needs more room."""
@@ -152,6 +165,8 @@ class Engine:
             context = self._context(entries, starts)
             if device_tokens is not None:
                 context.token_ids.copy_(device_tokens)
+            if context.all_single and self.attention_block_size:
+                context.decode_splits = self.decode_splits(len(entries), max(starts) + 1)
             logits = self.model.forward(context, self.cache)
         for entry, start in zip(entries, starts):
             self.cache.advance(entry.slot, start + len(entry.tokens))

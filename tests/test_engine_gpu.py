@@ -228,3 +228,19 @@ def test_plain_kernels_alone_give_the_same_logits(folders, which, dtype):
         for request, prompt_length, logits in zip(requests, [30, 3, 8], batched):
             assert relative_error(logits, expected(folders, which, dtype, request)[prompt_length - 1 :]) < TOLERANCE[dtype]
     assert relative_error(found[False][0], found[True][0]) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_a_given_attention_block_size_changes_no_logits(folders, which, dtype, graphs):
+    """`--attention-block-size`: the context of a decode step cut into blocks of 32 or of 256 positions, whatever the batch."""
+    vocab = tiny_configs.CONFIGS[which]["vocab_size"]
+    limit = tiny_configs.CONFIGS[which]["max_position_embeddings"]
+    (tokens,) = random_prompts(vocab, [min(limit, 200)], seed=43)
+    wanted = expected(folders, which, dtype, tokens)[-32:]
+    for block in (32, 256):
+        engine = engine_for(folders[(which, dtype)], dtype, "gpu", 1024)
+        engine.use_graphs = engine.use_graphs and graphs
+        engine.attention_block_size = block
+        assert engine.decode_splits(3, 200) == (8 if block == 32 else 1) and engine.decode_splits(1, 5000) == (64 if block == 32 else 32)
+        assert relative_error(run_tail_stepwise(engine, tokens, 32), wanted) < TOLERANCE[dtype]
