@@ -52,7 +52,7 @@ def build_parser() -> argparse.ArgumentParser:
     request.add_argument("--temperature", type=float, default=0.0, help="0: greedy. [default: 0]")
     request.add_argument("--stop-ids", default=None, metavar="1,2", help="Stop token ids. [default: eos_token_id of the folder]")
     logging = parser.add_argument_group("Logging options")
-    logging.add_argument("--metrics", action="store_true", help="Log throughput to stderr. [default: off]")
+    logging.add_argument("--metrics", action="store_true", help="Log live decode t/s to stderr. [default: off] Every ~5s during generation and at completion.")
     logging.add_argument("--tracing", action="store_true", help="Log numerical traces (token ids, logit checksums) to stdout. [default: off]")
     logging.add_argument("--vram-metrics", action="store_true", help="Sample process VRAM; log peak to stderr. [default: off] Independent of --metrics and --tracing.")
     return parser
@@ -146,6 +146,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     select = Sampler(SamplingParams(args.temperature, args.seed))   # the object, not its method: the loop then decodes one step ahead
     tracer = _Tracer(select) if args.tracing else None
     metrics = GenerationMetrics()
+    if args.metrics:   # live: every ~5 s during generation and at completion
+        metrics.log_interval_s = 5.0
+        metrics.sink = lambda record: print("inference_metrics " + json.dumps(record), file=sys.stderr, flush=True)
     memory = None
     if args.vram_metrics:
         from . import vram
@@ -157,6 +160,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     except Exception as error:
         if memory is not None:
             vram.report(memory.finish(), args.model, error=str(error))
+        if args.metrics:
+            metrics.sink(dict(metrics.report("error"), error=str(error)))
         raise
     elapsed = time.perf_counter() - started
     if memory is not None:
@@ -169,5 +174,5 @@ def main(argv: Optional[List[str]] = None) -> int:
             "schema": "tau_rs_b200/1", "prompts": prompts, "generated": [result.tokens for result in results], "steps": tracer.steps,
             "summary": {"decode_tokens_per_second": metrics.decode_tokens_per_second, "elapsed_ms": elapsed * 1e3}}))
     if args.metrics:
-        print("inference_metrics " + json.dumps(dict(metrics.as_dict(), elapsed_ms=round(elapsed * 1e3, 3))), file=sys.stderr)
+        metrics.sink(metrics.report("ok"))
     return 0

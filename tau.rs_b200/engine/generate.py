@@ -44,7 +44,11 @@ class GenerationResult:
 class GenerationMetrics:
     """Counters in the reference's sense (crates/metrics/src/serving.rs:35-54,84-93): the decode
     rate is decoded tokens over the summed time of decode steps; the token that prefill produces
-    and stop tokens are not decoded tokens."""
+    and stop tokens are not decoded tokens.
+
+    With `log_interval_s` and `sink`, a record with `status: "running"` goes to `sink` at a token boundary whenever
+    that many seconds have passed since the last one (serving.rs:56-58,92-95,160-165: every 5 s there, no thread of
+    its own); `interval_decode_tokens_per_second` is the rate of the decode work since the record before (:46-47)."""
 
     prompt_tokens: int = 0
     generated_tokens: int = 0
@@ -54,6 +58,29 @@ class GenerationMetrics:
     prefill_steps: int = 0
     decode_steps: int = 0
     batches: int = 0
+    log_interval_s: Optional[float] = None
+    sink: Optional[Callable[[dict], None]] = None
+    _started: float = field(default_factory=time.perf_counter, repr=False)
+    _last_reported: float = field(default_factory=time.perf_counter, repr=False)
+    _last_decode_tokens: int = field(default=0, repr=False)
+    _last_decode_ms: float = field(default=0.0, repr=False)
+
+    def report(self, status: str, now: Optional[float] = None) -> dict:
+        """The counters as one record; advances the interval's baseline."""
+        now = time.perf_counter() if now is None else now
+        tokens, span = self.decode_tokens - self._last_decode_tokens, self.decode_ms - self._last_decode_ms
+        record = dict(self.as_dict(), status=status, elapsed_ms=round((now - self._started) * 1e3, 3),
+                      interval_decode_tokens_per_second=round(tokens / (span / 1e3), 2) if tokens > 0 and span > 0 else None)
+        self._last_reported, self._last_decode_tokens, self._last_decode_ms = now, self.decode_tokens, self.decode_ms
+        return record
+
+    def tick(self, now: Optional[float] = None) -> None:
+        """Called at token boundaries of decoding: sends a progress record if one is due."""
+        if self.log_interval_s is None or self.sink is None:
+            return
+        now = time.perf_counter() if now is None else now
+        if now - self._last_reported >= self.log_interval_s:
+            self.sink(self.report("running", now))
 
     @property
     def decode_tokens_per_second(self) -> float:
@@ -214,6 +241,7 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
                 if token not in stop:
                     metrics.decode_tokens += 1
                 accept(item, token)
+            metrics.tick()
     finally:
         for item in list(live):
             backend.close_sequence(item.slot)
@@ -248,10 +276,13 @@ def _decode_ahead(backend, live, launch, collect, stop, accept, metrics) -> None
             if token not in stop:
                 metrics.decode_tokens += 1
             accept(item, token)
+        now = time.perf_counter()
+        metrics.decode_ms += (now - started) * 1e3
+        started = now
         if following is None:
             break
+        metrics.tick(now)
         items, pending = next_items, following
-    metrics.decode_ms += (time.perf_counter() - started) * 1e3
 
 
 def _take(tokens, rows):

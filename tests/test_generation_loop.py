@@ -283,3 +283,37 @@ def test_vram_sampler_keeps_start_peak_end_and_a_failed_sample():
     assert failed["status"] == "error" and failed["error"] == "out of pages"
     never = vram.VramSampler(lambda: (_ for _ in ()).throw(RuntimeError("no device")), "device", None, interval_ms=5).start().finish()
     assert never["vram_start_bytes"] is None and never["vram_peak_delta_bytes"] is None and never["vram_error"] == "no device"
+
+
+def test_metrics_send_a_progress_record_when_one_is_due():
+    """crates/metrics/src/serving.rs:92-95,160-165: checked at token boundaries, every 5 s; the interval's rate is the
+    decode work since the record before (:118-121), the request's rate is over all of it."""
+    records = []
+    metrics = GenerationMetrics(log_interval_s=5.0, sink=records.append)
+    begin = metrics._started
+    metrics.decode_tokens, metrics.decode_ms = 10, 1000.0
+    metrics.tick(begin + 1.0)
+    assert records == []
+    metrics.tick(begin + 5.5)
+    assert len(records) == 1 and records[0]["status"] == "running" and records[0]["decode_tokens_per_second"] == 10.0
+    assert records[0]["interval_decode_tokens_per_second"] == 10.0 and records[0]["elapsed_ms"] == 5500.0
+    metrics.decode_tokens, metrics.decode_ms = 40, 2000.0
+    metrics.tick(begin + 9.0)                     # 3.5 s after the last record
+    assert len(records) == 1
+    metrics.tick(begin + 10.6)
+    assert records[1]["interval_decode_tokens_per_second"] == 30.0 and records[1]["decode_tokens_per_second"] == 20.0
+    final = metrics.report("ok", begin + 11.0)
+    assert final["status"] == "ok" and final["interval_decode_tokens_per_second"] is None and final["decode_tokens"] == 40
+    silent = GenerationMetrics()
+    silent.tick(begin + 100.0)                    # no sink: nothing happens
+
+
+def test_the_loop_reports_progress_both_ways_of_decoding():
+    for ahead in (False, True):
+        records = []
+        metrics = GenerationMetrics(log_interval_s=0.0, sink=records.append)
+        backend = AheadBackend() if ahead else FakeBackend()
+        results = generate_tokens(backend, [[1, 2, 3], [4]], 5, TwoHalves() if ahead else select, (), 8, None, metrics)
+        assert [result.tokens for result in results] == [expected_tokens([1, 2, 3], 5), expected_tokens([4], 5)]
+        assert records and all(record["status"] == "running" for record in records)
+        assert records[-1]["decode_tokens"] <= metrics.decode_tokens == 8 and metrics.decode_ms > 0
