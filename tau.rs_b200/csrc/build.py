@@ -19,7 +19,7 @@ import sys
 import tempfile
 import threading
 import time
-from typing import Dict, Optional, Sequence
+from typing import Dict, Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -10,12 +10,11 @@ the device as one int32 buffer.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Sequence
 
 import numpy as np
 import torch
 
-from ..cache.sequence_cache import PAGE_TOKENS, pages_for
 
 
 @dataclass

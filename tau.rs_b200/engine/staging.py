@@ -6,7 +6,6 @@ host from ever waiting in practice.
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 

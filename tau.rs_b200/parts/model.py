@@ -7,7 +7,7 @@ run, in which order and on which cache layer is the spec's schedule, not code.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -15,7 +15,6 @@ from ..config.specs import ModelSpec
 from ..csrc import kernels
 from ..weights.tensor_spec import TensorSpec
 from .base import CacheNeed
-from .linear import StackedLinear
 from .registry import build
 
 

@@ -1,7 +1,7 @@
 """Shared by the tests: building engines on tiny folders, replaying requests in several cuttings."""
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import List, Sequence
 
 import numpy as np
 import torch

@@ -1,12 +1,11 @@
 """The engine on the GPU against the plain whole-sequence implementation, in every way of cutting the work."""
-import numpy as np
 import pytest
 import torch
 
 import plain_model
 import tiny_configs
 from helpers import (engine_for, plain_logits, random_prompts, relative_error, run_batched, run_tail_stepwise, run_whole)
-from tau_rs_b200 import StepEntry, generate, load_model
+from tau_rs_b200 import StepEntry, generate
 
 pytestmark = pytest.mark.gpu
 # Largest difference relative to the largest logit.  32-bit: rounding of sums only.  bfloat16: the plain

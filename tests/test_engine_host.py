@@ -4,14 +4,13 @@ What is tested here is packing, page and slot bookkeeping, the schedule and the 
 addressing, in every way of cutting the work; the CUDA kernels themselves are tested on the
 GPU.  Expected logits come from the plain whole-sequence implementation.
 """
-import numpy as np
 import pytest
 import torch
 
 import plain_kernels
 import tiny_configs
 from helpers import (engine_for, plain_logits, random_prompts, relative_error, run_batched, run_tail_stepwise, run_whole)
-from tau_rs_b200 import CacheFull, Engine, StepEntry, StepError, load_model
+from tau_rs_b200 import CacheFull, StepEntry, StepError
 
 
 @pytest.fixture

@@ -1,7 +1,5 @@
 """Each part alone against its plain function, and toy architectures assembled from parts that the test defines:
 a mixer with state of its own, a feed-forward with routing, another position encoding."""
-import json
-import math
 
 import numpy as np
 import pytest

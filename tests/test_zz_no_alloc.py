@@ -10,7 +10,6 @@ The file sorts last so that a run that stops at the first failure has run every 
 """
 import ctypes
 
-import numpy as np
 import pytest
 import torch
 
