@@ -317,3 +317,24 @@ def test_the_loop_reports_progress_both_ways_of_decoding():
         assert [result.tokens for result in results] == [expected_tokens([1, 2, 3], 5), expected_tokens([4], 5)]
         assert records and all(record["status"] == "running" for record in records)
         assert records[-1]["decode_tokens"] <= metrics.decode_tokens == 8 and metrics.decode_ms > 0
+
+
+def test_decode_split_rule_stays_within_what_the_kernel_and_the_machine_take():
+    """The number of context blocks of decode attention, for every batch and context: at least one block of 64 positions
+    each, never more blocks than are resident at once (592) unless one split is all there is, clusters of more than 8
+    only while they fill at most half of the places, at most 16 in a cluster and 32 at all; the same for every length of
+    a power-of-two bucket, because a captured graph is keyed by the bucket."""
+    from tau_rs_b200.csrc.kernels import decode_splits
+
+    for kv_blocks in (1, 2, 8, 16):
+        for n_seqs in (1, 2, 3, 4, 8, 13, 32, 64, 200):
+            for length in (1, 2, 63, 64, 65, 200, 1024, 2049, 4096, 8192, 8193, 32001, 131072):
+                splits = decode_splits(n_seqs, length, kv_blocks)
+                blocks = n_seqs * kv_blocks
+                bucket = 1 << max(0, (length - 1).bit_length())
+                assert 1 <= splits <= (16 if bucket <= 8192 else 32)
+                assert splits == 1 or (splits * 64 <= bucket and splits * blocks <= 592)
+                assert not (8 < splits <= 16) or blocks * splits <= 296
+                low = bucket // 2 + 1
+                assert decode_splits(n_seqs, low, kv_blocks) == splits == decode_splits(n_seqs, bucket, kv_blocks)
+    assert decode_splits(8, 2049, 8) == 8 and decode_splits(1, 2049, 8) == 16 and decode_splits(64, 2049, 8) == 1
