@@ -243,3 +243,47 @@ def test_a_given_attention_block_size_changes_no_logits(folders, which, dtype, g
         engine.attention_block_size = block
         assert engine.decode_splits(3, 200) == (8 if block == 32 else 1) and engine.decode_splits(1, 5000) == (64 if block == 32 else 32)
         assert relative_error(run_tail_stepwise(engine, tokens, 32), wanted) < TOLERANCE[dtype]
+
+
+MEDIUM = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 5000, "hidden_size": 1024, "intermediate_size": 3072,
+    "num_hidden_layers": 2, "num_attention_heads": 16, "num_key_value_heads": 8, "head_dim": 128, "attention_bias": False,
+    "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "max_position_embeddings": 2048, "tie_word_embeddings": True,
+    "hidden_act": "silu", "torch_dtype": "bfloat16", "eos_token_id": 1,
+}
+
+
+def test_fast_kernels_against_plain_kernels_at_the_width_of_a_real_model():
+    """The layer sizes of Qwen3-0.6B (two layers, a small vocabulary): the tiny configurations never reach the paired
+    256 x 256 tiles, the products cut along K, the tensor-memory attention or clusters of decode blocks inside the engine.
+    Prompts of 700 and 130 tokens, then decode batches of 1, 12 and 40 sequences; the plain kernels are the yardstick."""
+    from tau_rs_b200 import Engine
+    from tau_rs_b200.api import random_model
+    from tau_rs_b200.csrc import kernels
+
+    prompts = random_prompts(MEDIUM["vocab_size"], [700, 130] + [70] * 38, seed=51)
+    steps = 4
+    found = {}
+    try:
+        for optimized in (False, True):
+            kernels.prefer_optimized(optimized)
+            engine = Engine(random_model(MEDIUM, seed=9, dtype="bfloat16", norm_jitter=0.1), 64 * 128)
+            rows = []
+            for batch in ([0], list(range(1, 13)), list(range(40))):
+                slots = [engine.open_sequence() for _ in batch]
+                logits = engine.step([StepEntry(slot, prompts[i], [len(prompts[i]) - 1]) for slot, i in zip(slots, batch)])
+                rows.append(logits.float().cpu())
+                for step in range(steps):
+                    tokens = [int(prompts[i][step]) for i in batch]           # given tokens, so that both runs feed the same
+                    logits = engine.step([StepEntry(slot, [token], [0]) for slot, token in zip(slots, tokens)])
+                    rows.append(logits.float().cpu())
+                for slot in slots:
+                    engine.close_sequence(slot)
+                engine.cache.check()
+            found[optimized] = rows
+    finally:
+        kernels.prefer_optimized(True)
+    assert kernels.gemm_tc_status() == 0 and kernels.attention_prefill_tc_status(128) == 0
+    for fast, plain in zip(found[True], found[False]):
+        assert fast.shape == plain.shape and torch.isfinite(fast).all()
+        assert relative_error(fast, plain) < TOLERANCE["bfloat16"]
