@@ -253,21 +253,27 @@ MEDIUM = {
 }
 
 
-def test_fast_kernels_against_plain_kernels_at_the_width_of_a_real_model():
-    """The layer sizes of Qwen3-0.6B (two layers, a small vocabulary): the tiny configurations never reach the paired
+OTHER_MEDIUM = dict(MEDIUM, vocab_size=3001, hidden_size=768, intermediate_size=2056, num_attention_heads=12, num_key_value_heads=4,
+                    head_dim=64, attention_bias=True, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+
+
+@pytest.mark.parametrize("config", [MEDIUM, OTHER_MEDIUM], ids=["d128", "d64_bias_odd_vocab"])
+def test_fast_kernels_against_plain_kernels_at_the_width_of_a_real_model(config):
+    """The layer sizes of Qwen3-0.6B, and another set with heads of 64, biases, an intermediate width that is no multiple of 16
+    and an odd vocabulary (two layers, a small vocabulary): the tiny configurations never reach the paired
     256 x 256 tiles, the products cut along K, the tensor-memory attention or clusters of decode blocks inside the engine.
     Prompts of 700 and 130 tokens, then decode batches of 1, 12 and 40 sequences; the plain kernels are the yardstick."""
     from tau_rs_b200 import Engine
     from tau_rs_b200.api import random_model
     from tau_rs_b200.csrc import kernels
 
-    prompts = random_prompts(MEDIUM["vocab_size"], [700, 130] + [70] * 38, seed=51)
+    prompts = random_prompts(config["vocab_size"], [700, 130] + [70] * 38, seed=51)
     steps = 4
     found = {}
     try:
         for optimized in (False, True):
             kernels.prefer_optimized(optimized)
-            engine = Engine(random_model(MEDIUM, seed=9, dtype="bfloat16", norm_jitter=0.1), 64 * 128)
+            engine = Engine(random_model(config, seed=9, dtype="bfloat16", norm_jitter=0.1), 64 * 128)
             rows = []
             for batch in ([0], list(range(1, 13)), list(range(40))):
                 slots = [engine.open_sequence() for _ in batch]
@@ -283,7 +289,7 @@ def test_fast_kernels_against_plain_kernels_at_the_width_of_a_real_model():
             found[optimized] = rows
     finally:
         kernels.prefer_optimized(True)
-    assert kernels.gemm_tc_status() == 0 and kernels.attention_prefill_tc_status(128) == 0
+    assert kernels.gemm_tc_status() == 0 and kernels.attention_prefill_tc_status(config["head_dim"]) == 0
     for fast, plain in zip(found[True], found[False]):
         assert fast.shape == plain.shape and torch.isfinite(fast).all()
         assert relative_error(fast, plain) < TOLERANCE["bfloat16"]
