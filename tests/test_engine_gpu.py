@@ -293,3 +293,20 @@ def test_fast_kernels_against_plain_kernels_at_the_width_of_a_real_model(config)
     for fast, plain in zip(found[True], found[False]):
         assert fast.shape == plain.shape and torch.isfinite(fast).all()
         assert relative_error(fast, plain) < TOLERANCE["bfloat16"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_plain_implementation_at_the_width_of_a_real_model(tmp_path, dtype):
+    """One layer of the second set of sizes above against the plain whole-sequence implementation, in 32-bit and in
+    bfloat16: a prompt of 300 tokens whole, and its last 16 tokens one by one."""
+    from tau_rs_b200.weights import write_random_model
+
+    config = dict(OTHER_MEDIUM, num_hidden_layers=1, torch_dtype=dtype)
+    folder = str(tmp_path / "medium")
+    write_random_model(folder, config, seed=12, norm_jitter=0.1, storage=dtype)
+    (tokens,) = random_prompts(config["vocab_size"], [300], seed=52)
+    wanted = plain_logits(folder, tokens, bf16=dtype == "bfloat16")
+    engine = engine_for(folder, dtype, "gpu", 1024)
+    assert relative_error(run_whole(engine, tokens), wanted) < TOLERANCE[dtype]
+    assert relative_error(run_tail_stepwise(engine, tokens, 16), wanted[-16:]) < TOLERANCE[dtype]
+    engine.cache.check()
