@@ -427,13 +427,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             const bool grow = tile_max > used_max + kRescaleThreshold;     // true for the first key a row sees
             // The loads and stores of tensor memory are warp-wide, so the whole warp takes part if any of its rows grows.
             const bool rescale = grow && i > 0 && used_max != -INFINITY;
-            if (__any_sync(0xffffffffu, rescale)) {
-                // O must not be touched while the second product of the tile before is still writing it.  Only here: a warp
-                // whose maxima have settled never waits for that product, and its exponentials run beside it.  (The
-                // softmax is at most one tile ahead of the second products, so the phase waited for is the current one
-                // or the one just completed.)
+            // A wait on an mbarrier names a phase by its parity alone, so it tells apart only the phase in progress and the one
+            // before it.  While this warp works on tile i the second products of the tiles up to i - 2 are done (the scores of
+            // tile i were issued behind them) and that of tile i cannot have begun (it needs this warp's probabilities): the
+            // barrier is in phase i - 1 or i, and a wait for phase i - 1 is safe.  After the last tile's probabilities are
+            // handed over it may be in phase n - 2, n - 1 or n, which a wait for phase n - 1 cannot tell apart (in phase
+            // n - 2 it would pass at once, before the last two products): so the last tile always waits for phase n - 2
+            // first, which leaves n - 1 or n for the wait behind the loop.
+            const bool last_tile = i == n_tiles - 1 && i > 0;
+            if (__any_sync(0xffffffffu, rescale) || last_tile) {
+                // O must not be touched while the second product of the tile before is still writing it.  Only here (and
+                // at the last tile): a warp whose maxima have settled never waits for that product, and its exponentials
+                // run beside it.
                 if (!barrier_wait(&shared->pv_done, (i - 1) & 1u, abort_flag)) { alive = false; break; }
                 tensor_fence_after_sync();
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
                 const float factor = rescale ? exp2f(used_max - tile_max) : 1.0f;
                 sum *= factor;
                 float part[32];

@@ -310,3 +310,30 @@ def test_the_plain_implementation_at_the_width_of_a_real_model(tmp_path, dtype):
     assert relative_error(run_whole(engine, tokens), wanted) < TOLERANCE[dtype]
     assert relative_error(run_tail_stepwise(engine, tokens, 16), wanted[-16:]) < TOLERANCE[dtype]
     engine.cache.check()
+
+
+@pytest.mark.parametrize("length,config", [(5000, MEDIUM), (9000, OTHER_MEDIUM)], ids=["5000_d128", "9000_d64"])
+def test_a_long_context_at_the_width_of_a_real_model(tmp_path, length, config):
+    """One layer in bfloat16 over thousands of positions against the plain implementation: the prompt whole (dozens of
+    query tiles and up to 141 key tiles of the tensor-memory attention), then six tokens one by one over a context that
+    decode attention cuts into 16 blocks of one cluster (5,000 positions) or 32 that meet in global memory (9,000)."""
+    from tau_rs_b200.csrc import kernels
+    from tau_rs_b200.weights import write_random_model
+
+    config = dict(config, num_hidden_layers=1, max_position_embeddings=16384, torch_dtype="bfloat16")
+    folder = str(tmp_path / "long")
+    write_random_model(folder, config, seed=13, norm_jitter=0.1, storage="bfloat16")
+    (tokens,) = random_prompts(config["vocab_size"], [length + 6], seed=53)
+    wanted = plain_logits(folder, tokens, bf16=True)
+    engine = engine_for(folder, "bfloat16", "gpu", 64 * 160)
+    assert engine.decode_splits(1, length + 1) == (16 if length <= 8192 else 32)
+    slot = engine.open_sequence()
+    places = [0, 63, 64, length // 2, length - 2, length - 1]
+    logits = engine.step([StepEntry(slot, tokens[:length], places)]).float().cpu()
+    assert relative_error(logits, wanted[places]) < TOLERANCE["bfloat16"]
+    for index in range(length, length + 6):
+        logits = engine.step([StepEntry(slot, [tokens[index]], [0])]).float().cpu()
+        assert relative_error(logits, wanted[index : index + 1]) < TOLERANCE["bfloat16"]
+    engine.close_sequence(slot)
+    engine.cache.check()
+    assert kernels.attention_prefill_tc_status(config["head_dim"]) == 0 and kernels.gemm_tc_status() == 0
