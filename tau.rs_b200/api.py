@@ -64,14 +64,18 @@ def load_model(folder: str, dtype: str = "auto", device="gpu", enforce_declared_
 
 
 def random_model(config_json: dict, seed: int = 0, dtype: str = "bfloat16", device="gpu", norm_jitter: float = 0.0) -> DecoderModel:
-    """A model of the architecture that `config_json` names with random weights drawn on the device (no files)."""
+    """A model of the architecture that `config_json` names with random weights drawn on the device (no files).
+
+    The values are those that `write_random_model` writes for the same seed, tensor by tensor: a bfloat16 model here
+    equals a folder written with `storage="bfloat16"`, a float32 model one written with `storage="float32"`."""
     entry = architecture_for(config_json)
     spec = entry.build_spec(entry.parse_config(config_json))
     target = device if isinstance(device, torch.device) else resolve_device(device)
     run_dtype = _TORCH_DTYPE[canonical_dtype(dtype)]
     model = DecoderModel(spec, run_dtype, target)
-    for name, tensor, tensor_spec in random_tensors(model.tensor_specs(), seed, norm_jitter, device=target):
-        model.assign(name, tensor.to(device_dtype(tensor_spec, run_dtype)))
+    for name, tensor, _ in random_tensors(model.tensor_specs(), seed, norm_jitter, device=target,
+                                          dtype_of=lambda tensor_spec: device_dtype(tensor_spec, run_dtype)):
+        model.assign(name, tensor)
     model.finalize_weights()
     model.generation_config = GenerationConfig()
     return model

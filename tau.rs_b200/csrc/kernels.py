@@ -192,16 +192,30 @@ def _tc_fits(values, weight, out) -> bool:
             and values.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (of the current one if none is named; 148, a B200's, where there is no GPU
+    to ask, which only the host-side tests of the rules below meet)."""
+    if not torch.cuda.is_available():
+        return 148
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
 _tc_workspace = {}
-_TC_WORKSPACE_FLOATS = 2 * 148 * 128 * 128   # a 128 x 128 float partial for each of two blocks per SM: 19.4 MB
 _TC_TICKETS = 4096
 
 
 def _tc_workspace_for(device):
-    """The partial tiles and tickets of a product cut along K; one pair per device and stream order."""
+    """The partial tiles and tickets of a product cut along K; one pair per device and stream order.
+    A 128 x 128 float partial for each of two blocks per SM (19.4 MB on 148 SMs)."""
     entry = _tc_workspace.get(device)
     if entry is None:
-        entry = _tc_workspace[device] = (torch.empty(_TC_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+        entry = _tc_workspace[device] = (torch.empty(2 * sm_count(device) * 128 * 128, dtype=torch.float32, device=device),
                                          torch.zeros(_TC_TICKETS, dtype=torch.int32, device=device))   # zero once; the kernel leaves them at zero
     return entry
 
@@ -236,16 +250,6 @@ def gemm_tc(values, weight, bias, out, token_box: int = 0, gated: bool = False, 
 def gemm_tc_status() -> int:
     """0 unless a bounded wait inside the tensor-core product ran out (synchronises the device)."""
     return build.load_library("gemm_tc.cu").tau_gemm_tc_status()
-
-
-def gemm_library(values, weight, bias, out) -> None:
-    """bfloat16 product through the vendor library (cuBLAS by way of torch), as the reference's engine does for
-    its dense projections (crates/models/src/components/cuda/decode/operation.rs:150-193)."""
-    _on_device(values, weight, bias, out)
-    _require(values.dtype == weight.dtype == out.dtype == torch.bfloat16, "the library product is used for bfloat16 only")
-    torch.mm(values, weight.t(), out=out)
-    if bias is not None:
-        out.add_(bias.to(out.dtype))
 
 
 GATE_GROUP = 8   # rows of a gate (and of its up) that lie together in a weight prepared for `linear_gated`
@@ -342,7 +346,7 @@ def attention_generic(queries, keys, values, out, positions, token_seq, page_row
         ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention")
 
 
-def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
+def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8, sms: Optional[int] = None) -> int:
     """Number of context splits that decode attention uses for this many sequences of at most this length.
 
     `kv_blocks` is the number of blocks per sequence and split (KV heads times head passes).  Four blocks of the
@@ -356,10 +360,11 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8) -> int:
     positions: 40.4 us with 32, 54.9 us with 16 in a cluster).  The length is rounded up to a power of two first, so
     that a captured graph (whose key holds this number) serves a whole range of lengths.
     """
+    sms = sms or sm_count()
     bucket = 1 << max(0, (max_len - 1).bit_length())
     blocks = max(1, n_seqs * kv_blocks)
-    splits = max(1, min(592 // blocks, bucket // 64, 16 if bucket <= 8192 else 32))
-    if 8 < splits <= 16 and blocks * splits > 296:
+    splits = max(1, min(4 * sms // blocks, bucket // 64, 16 if bucket <= 8192 else 32))
+    if 8 < splits <= 16 and blocks * splits > 2 * sms:
         splits = 8
     return splits
 
@@ -518,6 +523,17 @@ def attention(queries, keys, values, out, step, page_rows, n_heads: int, n_kv_he
     attention_generic(queries, keys, values, out, step.positions, step.token_seq, page_rows, n_heads, n_kv_heads, head_dim, scale, window)
 
 
+# ---------------------------------------------------------------------------- random weights
+def random_normal(out: torch.Tensor, key0: int, key1: int, scale: float, shift: float) -> None:
+    """Fills `out` (contiguous, float32 or bfloat16) with `shift + scale * n`, n ~ N(0, 1) of the counter-based stream
+    `(key0, key1)`; the same bits as `weights.random_init.standard_normals` gives on the host."""
+    _on_device(out)
+    _require(out.is_contiguous(), "the output must be contiguous")
+    library = build.load_library("random_init.cu")
+    _check(library.tau_random_normal(_code(out), _pointer(out), ctypes.c_longlong(out.numel()), ctypes.c_uint(key0), ctypes.c_uint(key1),
+                                     ctypes.c_float(scale), ctypes.c_float(shift), _stream()), "random_normal")
+
+
 # ---------------------------------------------------------------------------- selection
 _select_scratch = {}
 
@@ -528,8 +544,8 @@ def _scratch_for(logits) -> torch.Tensor:
     words = library.tau_select_scratch_words(ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]))
     key = (logits.device, torch.cuda.current_stream().cuda_stream)
     scratch = _select_scratch.get(key)
-    if scratch is None or scratch.numel() < words:
-        scratch = _select_scratch[key] = torch.empty(max(words, 1024), dtype=torch.int32, device=logits.device)
+    if scratch is None or scratch.numel() < words:   # zero once: the tickets at its start; the kernel leaves them at zero
+        scratch = _select_scratch[key] = torch.zeros(max(words, 1 << 16), dtype=torch.int32, device=logits.device)
     return scratch
 
 
@@ -546,7 +562,8 @@ def argmax(logits, tokens, valid) -> None:
     scratch = _scratch_for(logits)
     library = build.load_library("sampling.cu")
     _check(library.tau_argmax(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
-                              ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax", 2)
+                              ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid), _stream()), "argmax",
+           -(-logits.shape[0] // 8192))
 
 
 def store_words_host(source, pinned_target) -> None:
@@ -571,4 +588,5 @@ def sample_gumbel(logits, tokens, valid, inverse_temperature: float, seed: int, 
     _check(library.tau_sample_gumbel(_pointer(logits), ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]), _pointer(scratch),
                                      ctypes.c_longlong(scratch.numel()), _pointer(tokens), _pointer(valid),
                                      ctypes.c_float(inverse_temperature), ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF),
-                                     _pointer(request_ids), _pointer(token_indices), _stream()), "sample_gumbel", 2)
+                                     _pointer(request_ids), _pointer(token_indices), _stream()), "sample_gumbel",
+           -(-logits.shape[0] // 8192))

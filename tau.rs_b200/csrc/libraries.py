@@ -12,6 +12,7 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("gemm_tc.cu", ()),
         ("attention_generic.cu", ()),
         ("sampling.cu", ()),
+        ("random_init.cu", ()),
         # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.
         *[("attention_decode.cu", (f"TAU_HEAD_DIM={head_dim}", f"TAU_DTYPE={dtype}"))
           for head_dim in (128, 16, 32, 48) for dtype in (0, 1)],

@@ -1,62 +1,57 @@
-// Token selection from 32-bit logits `[rows, vocab]`: greedy argmax and Gumbel-max temperature sampling.
+// Token selection from 32-bit logits `[rows, vocab]` in one launch: greedy argmax and Gumbel-max temperature sampling.
 //
-// Greedy follows crates/cuda-kernels/src/kernels/greedy_argmax.cu:19-31,65-94,101-117: every logit becomes an
-// integer key that orders like the 32-bit float total order, NaN never takes part, the higher token id wins
-// among equal keys, and a row of NaN only is reported as invalid.  Two launches: blocks over vocabulary chunks
-// write one candidate each to scratch memory, then one block per row merges them.  Rows are independent.
+// What is chosen is the reference's (crates/engine/src/generation.rs:81-95; crates/cuda-kernels/src/kernels/
+// greedy_argmax.cu:19-31): the greatest logit by the total order of 32-bit floats, NaN never chosen, the highest
+// token id among equal logits, and a row of NaN only reported as invalid.  How it is done is this library's own: a
+// logit and its token id are packed into one 64-bit word, `ordered(logit) << 32 | token id`, so that the greatest
+// word is the choice and the tie rule costs nothing; zero stands for "nothing to choose from" (a NaN).  The grid is
+// (vocabulary slices, rows).  A block reduces its slice to one word, stores it, and takes a ticket of its row; the
+// block that takes the last ticket of a row reduces the row's words and writes the token.  No block waits for another,
+// and one launch serves any number of rows.  The tickets start at zero and each row's last block puts its ticket back.
 //
 // Temperature sampling picks argmax(logit / T + g) with g = -log(-log u), u from Philox4x32-10 with counter
 // (token id, index of the token within its request, request number, 0) and the seed as key.
 #include "common.cuh"
+#include "sampling_static.h"
 
 namespace {
 
 constexpr unsigned kThreads = 256;
-constexpr unsigned kItemsPerBlock = 2048;
+constexpr unsigned kSliceItems = 2048;        // logits per block
+constexpr unsigned kTicketWords = 8192;       // the scratch begins with one ticket per row; a launch serves at most this many rows
+typedef unsigned long long Packed;
 
-struct Candidate {
-    unsigned key, token, valid;
-};
-
-__device__ __forceinline__ Candidate candidate_of(float value, unsigned token) {
+// Monotone map of the float total order onto unsigned integers: negative values have all bits flipped, others the sign bit.
+__device__ __forceinline__ Packed pack(float value, unsigned token) {
+    if (value != value) return 0ull;
     const unsigned bits = __float_as_uint(value);
-    if ((bits & 0x7fffffffu) > 0x7f800000u) return {0u, 0u, 0u};
-    return {bits ^ ((bits & 0x80000000u) ? 0xffffffffu : 0x80000000u), token, 1u};
+    const unsigned ordered = bits ^ (static_cast<unsigned>(static_cast<int>(bits) >> 31) | 0x80000000u);   // >= 0x007fffff for -inf
+    return (static_cast<Packed>(ordered) << 32) | token;
 }
 
-__device__ __forceinline__ Candidate better(Candidate a, Candidate b) {
-    if (!b.valid) return a;
-    if (!a.valid || b.key > a.key || (b.key == a.key && b.token > a.token)) return b;
-    return a;
-}
+__device__ __forceinline__ Packed greater_of(Packed a, Packed b) { return a > b ? a : b; }
 
-__device__ Candidate block_best(Candidate value, Candidate* partial) {
+__device__ __forceinline__ Packed warp_greatest(Packed value) {
 #pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) {
-        Candidate other = {__shfl_xor_sync(0xffffffffu, value.key, offset), __shfl_xor_sync(0xffffffffu, value.token, offset),
-                           __shfl_xor_sync(0xffffffffu, value.valid, offset)};
-        value = better(value, other);
-    }
-    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = value;
+    for (int offset = 16; offset > 0; offset >>= 1) value = greater_of(value, __shfl_xor_sync(0xffffffffu, value, offset));
+    return value;
+}
+
+// The block's greatest word, in every thread of warp 0.  `shared` holds one word per warp.
+__device__ __forceinline__ Packed block_greatest(Packed value, Packed* shared) {
+    value = warp_greatest(value);
+    __syncthreads();   // `shared` may still be read from an earlier call
+    if ((threadIdx.x & 31) == 0) shared[threadIdx.x >> 5] = value;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        value = threadIdx.x < kThreads / 32 ? partial[threadIdx.x] : Candidate{0u, 0u, 0u};
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            Candidate other = {__shfl_xor_sync(0xffffffffu, value.key, offset), __shfl_xor_sync(0xffffffffu, value.token, offset),
-                               __shfl_xor_sync(0xffffffffu, value.valid, offset)};
-            value = better(value, other);
-        }
-    }
-    return value;  // meaningful in thread 0
+    value = (threadIdx.x < kThreads / 32) ? shared[threadIdx.x] : 0ull;
+    return threadIdx.x < 32 ? warp_greatest(value) : 0ull;
 }
 
 __device__ __forceinline__ unsigned philox_first_word(unsigned c0, unsigned c1, unsigned c2, unsigned c3, unsigned k0, unsigned k1) {
 #pragma unroll
     for (int round = 0; round < 10; ++round) {
-        const unsigned long long p0 = 0xD2511F53ull * c0, p1 = 0xCD9E8D57ull * c2;
-        const unsigned hi0 = static_cast<unsigned>(p0 >> 32), lo0 = static_cast<unsigned>(p0);
-        const unsigned hi1 = static_cast<unsigned>(p1 >> 32), lo1 = static_cast<unsigned>(p1);
+        const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
         c0 = hi1 ^ c1 ^ k0;
         c1 = lo1;
         c2 = hi0 ^ c3 ^ k1;
@@ -67,84 +62,109 @@ __device__ __forceinline__ unsigned philox_first_word(unsigned c0, unsigned c1, 
     return c0;
 }
 
-// Score whose maximum is the chosen token.  NaN logits stay NaN and are left out by candidate_of.
-__device__ __forceinline__ float gumbel_score(float logit, float inverse_temperature, unsigned token, unsigned token_index,
-                                              unsigned request, unsigned seed_lo, unsigned seed_hi) {
-    const unsigned word = philox_first_word(token, token_index, request, 0u, seed_lo, seed_hi);
+struct Noise {
+    float inverse_temperature;
+    unsigned seed_lo, seed_hi, request, token_index;
+};
+
+// Score whose maximum is the chosen token.  A NaN logit stays NaN and packs to zero.
+template <bool Gumbel> __device__ __forceinline__ float score(float logit, unsigned token, const Noise& noise) {
+    if (!Gumbel) return logit;
+    const unsigned word = philox_first_word(token, noise.token_index, noise.request, 0u, noise.seed_lo, noise.seed_hi);
     const float u = (static_cast<float>(word >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), 24 bits
-    return logit * inverse_temperature - logf(-logf(u));
+    return logit * noise.inverse_temperature - logf(-logf(u));
 }
 
 template <bool Gumbel>
-__global__ void chunk_best_kernel(const float* __restrict__ logits, unsigned vocab, unsigned* __restrict__ scratch,
-                                  float inverse_temperature, unsigned seed_lo, unsigned seed_hi,
-                                  const int* __restrict__ request_ids, const int* __restrict__ token_indices) {
+__global__ void __launch_bounds__(kThreads) select_kernel(const float* __restrict__ logits, unsigned vocab, Packed* slices, unsigned* tickets,
+                                                          int* __restrict__ tokens, int* __restrict__ valid, float inverse_temperature,
+                                                          unsigned seed_lo, unsigned seed_hi, const int* __restrict__ request_ids,
+                                                          const int* __restrict__ token_indices) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ Candidate partial[kThreads / 32];
-    const unsigned row = blockIdx.y;
+    __shared__ Packed shared[kThreads / 32];
+    __shared__ unsigned is_last;
+    const unsigned row = blockIdx.y, n_slices = gridDim.x;
     const float* row_logits = logits + static_cast<size_t>(row) * vocab;
-    Candidate best{0u, 0u, 0u};
-    const unsigned first = blockIdx.x * kItemsPerBlock;
-    const unsigned last = min(vocab, first + kItemsPerBlock);
-    unsigned request = 0, token_index = 0;
+    Noise noise = {inverse_temperature, seed_lo, seed_hi, 0u, 0u};
     if (Gumbel) {
-        request = static_cast<unsigned>(request_ids[row]);
-        token_index = static_cast<unsigned>(token_indices[row]);
+        noise.request = static_cast<unsigned>(request_ids[row]);
+        noise.token_index = static_cast<unsigned>(token_indices[row]);
     }
-    for (unsigned index = first + threadIdx.x; index < last; index += kThreads) {
-        float value = row_logits[index];
-        if (Gumbel) value = gumbel_score(value, inverse_temperature, index, token_index, request, seed_lo, seed_hi);
-        best = better(best, candidate_of(value, index));
+    const unsigned first = blockIdx.x * kSliceItems, last = min(vocab, first + kSliceItems);
+    Packed best = 0ull;
+    if ((reinterpret_cast<uintptr_t>(row_logits) & 15u) == 0) {   // rows that start on 16 bytes are read four logits at a time
+        const unsigned whole = first + ((last - first) & ~3u);
+        for (unsigned index = first + threadIdx.x * 4; index < whole; index += kThreads * 4) {
+            const float4 four = *reinterpret_cast<const float4*>(row_logits + index);
+            best = greater_of(best, pack(score<Gumbel>(four.x, index, noise), index));
+            best = greater_of(best, pack(score<Gumbel>(four.y, index + 1, noise), index + 1));
+            best = greater_of(best, pack(score<Gumbel>(four.z, index + 2, noise), index + 2));
+            best = greater_of(best, pack(score<Gumbel>(four.w, index + 3, noise), index + 3));
+        }
+        for (unsigned index = whole + threadIdx.x; index < last; index += kThreads)
+            best = greater_of(best, pack(score<Gumbel>(row_logits[index], index, noise), index));
+    } else {
+        for (unsigned index = first + threadIdx.x; index < last; index += kThreads)
+            best = greater_of(best, pack(score<Gumbel>(row_logits[index], index, noise), index));
     }
-    best = block_best(best, partial);
+    best = block_greatest(best, shared);
     if (threadIdx.x == 0) {
-        unsigned* slot = scratch + (static_cast<size_t>(row) * gridDim.x + blockIdx.x) * 3;
-        slot[0] = best.key;
-        slot[1] = best.token;
-        slot[2] = best.valid;
+        slices[static_cast<size_t>(row) * n_slices + blockIdx.x] = best;
+        __threadfence();                                            // the word is visible before the ticket is
+        is_last = atomicAdd(&tickets[row], 1u) == n_slices - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const volatile Packed* row_slices = slices + static_cast<size_t>(row) * n_slices;
+    best = 0ull;
+    for (unsigned index = threadIdx.x; index < n_slices; index += kThreads) best = greater_of(best, row_slices[index]);
+    best = block_greatest(best, shared);
+    if (threadIdx.x == 0) {   // both are always written, so that a row of NaN does not keep an earlier call's token
+        tokens[row] = static_cast<int>(static_cast<unsigned>(best));
+        valid[row] = best != 0ull;
+        tickets[row] = 0u;    // as the next call expects it
     }
 }
 
-__global__ void merge_best_kernel(const unsigned* __restrict__ scratch, unsigned chunks, int* __restrict__ tokens,
-                                  int* __restrict__ valid) {
-    grid_dependents_launch();
-    grid_dependency_wait();
-    __shared__ Candidate partial[kThreads / 32];
-    const unsigned row = blockIdx.x;
-    const unsigned* row_scratch = scratch + static_cast<size_t>(row) * chunks * 3;
-    Candidate best{0u, 0u, 0u};
-    for (unsigned index = threadIdx.x; index < chunks; index += kThreads)
-        best = better(best, {row_scratch[index * 3], row_scratch[index * 3 + 1], row_scratch[index * 3 + 2]});
-    best = block_best(best, partial);
-    if (threadIdx.x == 0) {  // both words are always written, also when every logit was NaN
-        tokens[row] = static_cast<int>(best.token);
-        valid[row] = static_cast<int>(best.valid);
-    }
-}
+unsigned slice_count(unsigned vocab) { return (vocab + kSliceItems - 1) / kSliceItems; }
 
-unsigned chunk_count(unsigned vocab) { return (vocab + kItemsPerBlock - 1) / kItemsPerBlock; }
+template <bool Gumbel>
+int launch_select(const float* logits, int rows, int vocab, Packed* slices, unsigned* tickets, int* tokens, int* valid, float inverse_temperature,
+                  unsigned long long seed, const int* request_ids, const int* token_indices, cudaStream_t stream) {
+    const unsigned n_slices = slice_count(static_cast<unsigned>(vocab));
+    for (int begin = 0; begin < rows; begin += kTicketWords) {      // one launch unless there are more rows than tickets
+        const int count = rows - begin < static_cast<int>(kTicketWords) ? rows - begin : static_cast<int>(kTicketWords);
+        tau_launch(select_kernel<Gumbel>, dim3(n_slices, count), dim3(kThreads), 0, stream, logits + static_cast<size_t>(begin) * vocab,
+                   static_cast<unsigned>(vocab), slices, tickets, tokens + begin, valid + begin, inverse_temperature,
+                   static_cast<unsigned>(seed), static_cast<unsigned>(seed >> 32), Gumbel ? request_ids + begin : nullptr,
+                   Gumbel ? token_indices + begin : nullptr);
+        const int status = tau_launch_status();
+        if (status) return status;
+    }
+    return 0;
+}
 
 }  // namespace
 
-// Scratch words (uint32) that a selection over `rows` x `vocab` needs.
+// Scratch words (uint32) that a selection over `rows` x `vocab` needs: the tickets, then one 64-bit word per row and
+// slice.  The first 8,192 words (the tickets) must be zero before the first call and are zero again after every call;
+// the rest may hold anything.
 TAU_EXPORT long long tau_select_scratch_words(int rows, int vocab) {
     if (rows <= 0 || vocab <= 0) return 0;
-    return static_cast<long long>(rows) * chunk_count(static_cast<unsigned>(vocab)) * 3;
+    const long long live_rows = rows < static_cast<int>(kTicketWords) ? rows : kTicketWords;
+    return kTicketWords + live_rows * slice_count(static_cast<unsigned>(vocab)) * 2;
 }
 
 TAU_EXPORT int tau_argmax(const float* logits, int rows, int vocab, unsigned* scratch, long long scratch_words, int* tokens,
                           int* valid, void* stream) {
     if (rows <= 0) return 0;
-    if (!logits || !scratch || !tokens || !valid || vocab <= 0 || scratch_words < tau_select_scratch_words(rows, vocab))
+    if (!logits || !scratch || !tokens || !valid || vocab <= 0 || scratch_words < tau_select_scratch_words(rows, vocab) ||
+        (reinterpret_cast<uintptr_t>(scratch) & 7u))
         return cudaErrorInvalidValue;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
-    tau_launch(chunk_best_kernel<false>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
-    int status = tau_launch_status();
-    if (status) return status;
-    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
-    return tau_launch_status();
+    return launch_select<false>(logits, rows, vocab, reinterpret_cast<Packed*>(scratch + kTicketWords), scratch, tokens, valid, 0.0f, 0ull,
+                                nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 TAU_EXPORT int tau_sample_gumbel(const float* logits, int rows, int vocab, unsigned* scratch, long long scratch_words,
@@ -152,33 +172,11 @@ TAU_EXPORT int tau_sample_gumbel(const float* logits, int rows, int vocab, unsig
                                  const int* request_ids, const int* token_indices, void* stream) {
     if (rows <= 0) return 0;
     if (!logits || !scratch || !tokens || !valid || !request_ids || !token_indices || vocab <= 0 ||
-        !(inverse_temperature > 0.0f) || scratch_words < tau_select_scratch_words(rows, vocab))
+        !(inverse_temperature > 0.0f) || scratch_words < tau_select_scratch_words(rows, vocab) || (reinterpret_cast<uintptr_t>(scratch) & 7u))
         return cudaErrorInvalidValue;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
-    tau_launch(chunk_best_kernel<true>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, inverse_temperature,
-                                                                   static_cast<unsigned>(seed), static_cast<unsigned>(seed >> 32),
-                                                                   request_ids, token_indices);
-    int status = tau_launch_status();
-    if (status) return status;
-    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
-    return tau_launch_status();
+    return launch_select<true>(logits, rows, vocab, reinterpret_cast<Packed*>(scratch + kTicketWords), scratch, tokens, valid,
+                               inverse_temperature, seed, request_ids, token_indices, static_cast<cudaStream_t>(stream));
 }
-
-// ---------------------------------------------------------------------------------------------------
-// The variant that allocates nothing (declared and described in sampling_static.h).
-#include "sampling_static.h"
-
-namespace {
-
-// Scratch of the static variant.  In host code this name is only a stand-in for the symbol: the device
-// address comes from cudaGetSymbolAddress, once per device, and that address is what the kernels get.
-static __device__ __align__(256) unsigned static_scratch[TAU_ARGMAX_STATIC_WORDS];
-
-constexpr int kMaxDevices = 64;
-unsigned* static_scratch_address[kMaxDevices] = {};
-
-}  // namespace
 
 namespace {
 // A few words from device memory into pinned host memory, stored by the kernel itself: a copy by the copy engine in the
@@ -204,7 +202,29 @@ TAU_EXPORT int tau_store_words_host(const int* source, int* pinned_target, int c
     return tau_launch_status();
 }
 
-TAU_EXPORT long long tau_argmax_static_words_needed(int rows, int vocab) { return tau_select_scratch_words(rows, vocab); }
+// ---------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in sampling_static.h).
+namespace {
+
+// Scratch of the static variant: 8,192 tickets, then 8,192 64-bit words.  A call that passes the size rule below has at
+// most 8,192 rows and at most 8,192 (row, slice) pairs, so both halves are large enough.  The array is zero when the
+// library is loaded, which is what the tickets need; the kernel puts every ticket back to zero.
+// In host code this name is only a stand-in for the symbol: the device address comes from cudaGetSymbolAddress,
+// once per device, and that address is what the kernel gets.
+static __device__ __align__(256) unsigned static_scratch[TAU_ARGMAX_STATIC_WORDS];
+static_assert(TAU_ARGMAX_STATIC_WORDS == kTicketWords * 3, "tickets and 64-bit words share the array as 1 : 2");
+
+constexpr int kMaxDevices = 64;
+unsigned* static_scratch_address[kMaxDevices] = {};
+
+long long static_words_needed(int rows, int vocab) {
+    if (rows <= 0 || vocab <= 0) return 0;
+    return static_cast<long long>(rows) * slice_count(static_cast<unsigned>(vocab)) * 3;
+}
+
+}  // namespace
+
+TAU_EXPORT long long tau_argmax_static_words_needed(int rows, int vocab) { return static_words_needed(rows, vocab); }
 
 TAU_EXPORT const char* tau_argmax_static_error(int code) {
     switch (code) {
@@ -218,7 +238,7 @@ TAU_EXPORT const char* tau_argmax_static_error(int code) {
 
 TAU_EXPORT int tau_argmax_static(const float* logits, int rows, int vocab, int* tokens, int* valid, void* stream) {
     if (!logits || !tokens || !valid || rows <= 0 || vocab <= 0) return TAU_ARGMAX_STATIC_BAD_ARGUMENT;
-    if (tau_select_scratch_words(rows, vocab) > TAU_ARGMAX_STATIC_WORDS) return TAU_ARGMAX_STATIC_TOO_LARGE;
+    if (static_words_needed(rows, vocab) > TAU_ARGMAX_STATIC_WORDS) return TAU_ARGMAX_STATIC_TOO_LARGE;
     int device = -1;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return static_cast<int>(status);
@@ -231,11 +251,9 @@ TAU_EXPORT int tau_argmax_static(const float* logits, int rows, int vocab, int* 
     }
     unsigned* scratch = static_scratch_address[device];
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const unsigned chunks = chunk_count(static_cast<unsigned>(vocab));
-    // Writes scratch[0 .. rows * chunks * 3): every word that the merge below reads.
-    tau_launch(chunk_best_kernel<false>, dim3(dim3(chunks, rows)), dim3(kThreads), 0, s, logits, vocab, scratch, 0.0f, 0u, 0u, nullptr, nullptr);
-    int launched = tau_launch_status();
-    if (launched) return launched;
-    tau_launch(merge_best_kernel, dim3(rows), dim3(kThreads), 0, s, scratch, chunks, tokens, valid);
-    return tau_launch_status();
+    status = cudaMemsetAsync(scratch, 0, sizeof(unsigned) * rows, s);   // the tickets of this call's rows; no allocation
+    if (status != cudaSuccess) return static_cast<int>(status);
+    // One launch.  Every 64-bit word that a row's last block reads has been written by a block of this call.
+    return launch_select<false>(logits, rows, vocab, reinterpret_cast<Packed*>(scratch + kTicketWords), scratch, tokens, valid, 0.0f, 0ull,
+                                nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }

@@ -27,11 +27,13 @@
  *     TAU_ARGMAX_STATIC_TOO_LARGE and nothing is launched.  64 rows of a 262,144-token vocabulary fit.
  *   - The first call on each device looks up the array's device address (with that device current)
  *     and remembers it.  Make that first call before any stream capture begins.
- *   - All calls share the one array, and it keeps what the last call wrote.  Nothing in it has to
- *     start at zero: the first kernel of a call writes every word that the second kernel of the
- *     same call reads.  Two calls that can run at the same time on one GPU (different streams with
- *     no ordering between them) race on the array; order them, or use `tau_argmax` with a scratch
- *     buffer per stream.
+ *   - All calls share the one array, and it keeps what the last call wrote.  Its first third holds one
+ *     ticket per row, which must be zero when a call's kernel starts: the array is zero when the library
+ *     is loaded, every call clears the tickets of its rows in stream order before its kernel (a
+ *     cudaMemsetAsync, which allocates nothing), and the kernel puts them back to zero.  The rest may hold
+ *     anything: every word of it that the call reads has been written by the same call.  Two calls that
+ *     can run at the same time on one GPU (different streams with no ordering between them) race on the
+ *     array; order them, or use `tau_argmax` with a scratch buffer per stream.
  *   - No cudaMalloc, cudaFree or other allocating routine is called, on any call.
  */
 #pragma once

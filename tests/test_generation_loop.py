@@ -320,21 +320,23 @@ def test_the_loop_reports_progress_both_ways_of_decoding():
 
 
 def test_decode_split_rule_stays_within_what_the_kernel_and_the_machine_take():
-    """The number of context blocks of decode attention, for every batch and context: at least one block of 64 positions
-    each, never more blocks than are resident at once (592) unless one split is all there is, clusters of more than 8
-    only while they fill at most half of the places, at most 16 in a cluster and 32 at all; the same for every length of
-    a power-of-two bucket, because a captured graph is keyed by the bucket."""
+    """The number of context blocks of decode attention, for every batch and context and for machines of several sizes:
+    at least one block of 64 positions each, never more blocks than are resident at once (four per SM) unless one split
+    is all there is, clusters of more than 8 only while they fill at most half of the places, at most 16 in a cluster and
+    32 at all; the same for every length of a power-of-two bucket, because a captured graph is keyed by the bucket."""
     from tau_rs_b200.csrc.kernels import decode_splits
 
-    for kv_blocks in (1, 2, 8, 16):
-        for n_seqs in (1, 2, 3, 4, 8, 13, 32, 64, 200):
-            for length in (1, 2, 63, 64, 65, 200, 1024, 2049, 4096, 8192, 8193, 32001, 131072):
-                splits = decode_splits(n_seqs, length, kv_blocks)
-                blocks = n_seqs * kv_blocks
-                bucket = 1 << max(0, (length - 1).bit_length())
-                assert 1 <= splits <= (16 if bucket <= 8192 else 32)
-                assert splits == 1 or (splits * 64 <= bucket and splits * blocks <= 592)
-                assert not (8 < splits <= 16) or blocks * splits <= 296
-                low = bucket // 2 + 1
-                assert decode_splits(n_seqs, low, kv_blocks) == splits == decode_splits(n_seqs, bucket, kv_blocks)
-    assert decode_splits(8, 2049, 8) == 8 and decode_splits(1, 2049, 8) == 16 and decode_splits(64, 2049, 8) == 1
+    for sms in (148, 132, 16):
+        for kv_blocks in (1, 2, 8, 16):
+            for n_seqs in (1, 2, 3, 4, 8, 13, 32, 64, 200):
+                for length in (1, 2, 63, 64, 65, 200, 1024, 2049, 4096, 8192, 8193, 32001, 131072):
+                    splits = decode_splits(n_seqs, length, kv_blocks, sms)
+                    blocks = n_seqs * kv_blocks
+                    bucket = 1 << max(0, (length - 1).bit_length())
+                    assert 1 <= splits <= (16 if bucket <= 8192 else 32)
+                    assert splits == 1 or (splits * 64 <= bucket and splits * blocks <= 4 * sms)
+                    assert not (8 < splits <= 16) or blocks * splits <= 2 * sms
+                    low = bucket // 2 + 1
+                    assert decode_splits(n_seqs, low, kv_blocks, sms) == splits == decode_splits(n_seqs, bucket, kv_blocks, sms)
+    assert decode_splits(8, 2049, 8, 148) == 8 and decode_splits(1, 2049, 8, 148) == 16 and decode_splits(64, 2049, 8, 148) == 1
+    assert decode_splits(8, 2049, 8, 132) == 8 and decode_splits(8, 2049, 8, 74) == 4

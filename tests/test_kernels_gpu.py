@@ -491,3 +491,62 @@ def test_gumbel_sampling_matches_plain_and_distribution():
     counts = torch.bincount(draws.long().cpu(), minlength=5).double() / 4000
     expected = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0, float("-inf")]).double() / 0.5, dim=0)
     assert float((counts - expected).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("count,scale,shift", [(1, 0.02, 0.0), (5, 0.02, 0.0), (4099, 0.1, 1.0), (3_000_001, 0.02, 0.0)])
+def test_random_weights_are_the_same_bits_on_the_device_and_on_the_host(dtype, count, scale, shift):
+    """The device's draw of a tensor against the host's (numpy): every bit equal, in float32 and after the rounding to
+    bfloat16, for counts that are no multiple of four and for both kinds of tensor (N(0, s) and 1 + N(0, s))."""
+    from tau_rs_b200.weights import TensorSpec, random_tensor
+
+    spec = TensorSpec((count,), role="vector" if shift else "matrix", init="ones" if shift else "normal", std=scale)
+    host = random_tensor("model.layers.3.some.weight", spec, seed=11, norm_jitter=scale, device="cpu", dtype=dtype)
+    device = random_tensor("model.layers.3.some.weight", spec, seed=11, norm_jitter=scale, device=DEVICE, dtype=dtype)
+    assert device.dtype == dtype and device.is_cuda
+    assert torch.equal(device.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       host.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    other = random_tensor("model.layers.4.some.weight", spec, seed=11, norm_jitter=scale, device=DEVICE, dtype=dtype)
+    assert count < 5 or not torch.equal(other, device)
+
+
+def test_a_model_drawn_on_the_device_equals_the_folder_written_on_the_host(tmp_path):
+    """`random_model` (no file) against `write_random_model` + `load_model` for the same configuration and seed."""
+    import tiny_configs
+    from tau_rs_b200 import load_model
+    from tau_rs_b200.api import random_model
+
+    for which, dtype in (("B", "float32"), ("C", "bfloat16")):
+        folder = tiny_configs.write_tiny(str(tmp_path), which, dtype)
+        loaded = load_model(folder, dtype, "gpu")
+        drawn = random_model(dict(tiny_configs.CONFIGS[which], torch_dtype=dtype), seed=tiny_configs.SEEDS[which], dtype=dtype, norm_jitter=0.1)
+        assert torch.equal(loaded.embedding, drawn.embedding) and torch.equal(loaded.head, drawn.head)
+        for a, b in zip(loaded.blocks, drawn.blocks):
+            assert torch.equal(a.mixer.qkv.weight, b.mixer.qkv.weight) and torch.equal(a.mixer.q_norm.weight, b.mixer.q_norm.weight)
+            assert torch.equal(a.feed_forward.gate_up.weight, b.feed_forward.gate_up.weight)
+            assert torch.equal(a.feed_forward.down.weight, b.feed_forward.down.weight)
+            if a.mixer.qkv.bias is not None:
+                assert torch.equal(a.mixer.qkv.bias, b.mixer.qkv.bias)
+
+
+def test_argmax_calls_in_a_row_share_their_scratch():
+    """Calls of changing sizes one after another on one stream (the tickets at the start of the scratch go back to zero
+    after every call), rows of NaN between valid ones (no token of an earlier call survives: crates/engine/src/
+    generation/greedy/tests.rs:125-156), and more rows than one launch has tickets for."""
+    generator = torch.Generator().manual_seed(60)
+    for rows, vocab in ((3, 5000), (64, 151936), (1, 7), (9000, 40), (3, 5000), (2, 4099)):
+        logits = torch.randn(rows, vocab, generator=generator)
+        logits[rows // 2, :] = float("nan")
+        logits[0, -1] = logits[0].max()
+        device_logits = logits.to(DEVICE)
+        tokens = torch.full((rows,), -7, dtype=torch.int32, device=DEVICE)
+        valid = torch.full((rows,), -7, dtype=torch.int32, device=DEVICE)
+        for _ in range(2):
+            kernels.argmax(device_logits, tokens, valid)
+        wanted = torch.where(torch.isnan(logits), torch.full_like(logits, -float("inf")), logits)
+        best = wanted.max(dim=1, keepdim=True).values
+        last_best = (vocab - 1) - torch.flip(wanted == best, dims=[1]).int().argmax(dim=1)
+        is_valid = ~torch.isnan(logits).all(dim=1)
+        assert torch.equal(valid.cpu().bool(), is_valid)
+        assert torch.equal(tokens.cpu()[is_valid].long(), last_best[is_valid])
+        assert int(tokens[rows // 2]) == 0 and int(valid[rows // 2]) == 0

@@ -121,3 +121,40 @@ def test_sharded_folders_and_broken_files(tmp_path):
     (empty / "model.safetensors").write_bytes(b"\xff" * 12)
     with pytest.raises(ModelLoadError):
         SafetensorsFolder(str(empty))
+
+
+def test_the_counter_based_stream():
+    """Philox4x32-10 against its published known answer for a counter and key of zero, and
+    the normal values against a double-precision Box-Muller of the same words; a tensor's values depend on the seed and
+    its name only, and a tensor drawn in pieces equals the tensor drawn whole."""
+    import numpy as np
+
+    from tau_rs_b200.weights.random_init import _draw_on_host, philox4x32, standard_normals, stream_key
+
+    def words(counter0, key0, key1):
+        return [int(word[0]) for word in philox4x32(np.array([counter0], dtype=np.uint64), key0, key1)]
+
+    assert words(0, 0, 0) == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    key = stream_key(0, "model.norm.weight")
+    assert key != stream_key(1, "model.norm.weight") and key != stream_key(0, "model.norm.weigh")
+    values = standard_normals(400_003, *key)
+    assert values.dtype == np.float32 and np.isfinite(values).all()
+    assert abs(float(values.mean())) < 0.01 and abs(float(values.std()) - 1.0) < 0.01
+    assert abs(float(((values - values.mean()) ** 4).mean() / values.var() ** 2) - 3.0) < 0.05
+    w0, w1, w2, w3 = philox4x32(np.arange(2000, dtype=np.uint64), *key)
+    for first, (radius_word, angle_word) in ((0, (w0, w1)), (2, (w2, w3))):
+        u = ((radius_word >> np.uint64(9)).astype(np.float64) + 0.5) * 2.0 ** -23
+        angle = ((angle_word >> np.uint64(9)).astype(np.float64) + 0.5) * 2.0 ** -23 * 2 * np.pi
+        radius = np.sqrt(-2 * np.log(u))
+        assert np.abs(values[first:8000:4] - radius * np.cos(angle)).max() < 2e-6
+        assert np.abs(values[first + 1:8000:4] - radius * np.sin(angle)).max() < 2e-6
+    assert np.array_equal(standard_normals(1000, *key, first_block=25), values[100:1100])
+    import tau_rs_b200.weights.random_init as random_init
+
+    whole = _draw_on_host(10_001, *key, 0.02, 0.0)
+    old = random_init._HOST_CHUNK
+    try:
+        random_init._HOST_CHUNK = 4096
+        assert np.array_equal(_draw_on_host(10_001, *key, 0.02, 0.0), whole)
+    finally:
+        random_init._HOST_CHUNK = old
