@@ -77,26 +77,51 @@ def read_prompt_file(path: str) -> List[List[int]]:
         raise SystemExit(f"--prompt-file {path}: expected a JSON list of lists of token ids, or one prompt of ids a line ({error})")
 
 
-class _Tracer:
-    """Wraps a selector: copies each step's logits to the host and records what the reference's trace records."""
+def logit_snapshot(values, token: int) -> dict:
+    """What the reference's trace keeps of one vector of logits (crates/metrics/src/logits.rs:10-60): the count, how many
+    are finite, the SHA-256 of all of them as little-endian 32-bit floats, up to 16 samples spread evenly over the
+    vocabulary (`token_id = i * (count - 1) / (samples - 1)`; a value that is not finite is null) and the chosen logit."""
+    import numpy as np
 
-    def __init__(self, select):
+    values = np.ascontiguousarray(values, dtype="<f4")
+    count = int(values.size)
+    finite = np.isfinite(values)
+    sample_count = min(count, 16)
+    samples = []
+    for i in range(sample_count):
+        token_id = i * max(count - 1, 0) // max(sample_count - 1, 1)
+        samples.append({"token_id": token_id, "value": float(values[token_id]) if finite[token_id] else None})
+    selected = float(values[token]) if 0 <= token < count and finite[token] else None
+    return {"count": count, "finite_count": int(finite.sum()), "sha256_f32_le": hashlib.sha256(values.tobytes()).hexdigest(),
+            "samples": samples, "selected_logit": selected}
+
+
+class _Tracer:
+    """Wraps a selector: copies each step's logits to the host and records what the reference's trace records for a
+    step (crates/metrics/src/trace.rs:88-106): its phase, the cache offset it ran at (0 for the prompt, then
+    `prompt + tokens so far - 1`, crates/engine/src/model_engine/generation.rs:181-183), how many tokens it brought,
+    the chosen token, whether that is a stop token, when it started and how long it took, and the logits' snapshot."""
+
+    def __init__(self, select, prompts, stop):
         self.select, self.steps, self.started = select, [], time.perf_counter()
+        self.prompts, self.stop = prompts, frozenset(stop)
+        self.boundary = self.started
 
     def __call__(self, logits, request_ids, token_indices):
-        begin = time.perf_counter()
+        begin = self.boundary
         tokens = self.select(logits, request_ids, token_indices)
         host = logits.float().cpu().numpy()
+        end = time.perf_counter()
         for row, (request, index, token) in enumerate(zip(request_ids, token_indices, tokens)):
-            values = host[row]
-            finite = values[values == values]
+            prompt_tokens = len(self.prompts[request])
             self.steps.append({
                 "index": len(self.steps), "request": request, "phase": "prefill" if index == 0 else "decode", "token_index": index,
-                "token_id": int(token), "start_us": int((begin - self.started) * 1e6),
-                "logits": {"count": int(values.size), "finite_count": int((abs(finite) != float("inf")).sum()),
-                           "sha256_f32_le": hashlib.sha256(values.astype("<f4").tobytes()).hexdigest(),
-                           "selected_logit": float(values[token])},
+                "cache_offset": 0 if index == 0 else prompt_tokens + index - 1, "input_tokens": prompt_tokens if index == 0 else 1,
+                "token_id": int(token), "is_eos": int(token) in self.stop,
+                "start_us": round((begin - self.started) * 1e6, 1), "duration_us": round((end - begin) * 1e6, 1),
+                "logits": logit_snapshot(host[row], int(token)),
             })
+        self.boundary = time.perf_counter()
         return tokens
 
 
@@ -144,7 +169,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     engine.use_graphs = engine.use_graphs and args.cuda_graph == "full"
     engine.attention_block_size = args.attention_block_size
     select = Sampler(SamplingParams(args.temperature, args.seed))   # the object, not its method: the loop then decodes one step ahead
-    tracer = _Tracer(select) if args.tracing else None
+    tracer = _Tracer(select, prompts, stop) if args.tracing else None
     metrics = GenerationMetrics()
     if args.metrics:   # live: every ~5 s during generation and at completion
         metrics.log_interval_s = 5.0

@@ -144,3 +144,41 @@ def windowed_cache_matches_whole_prompt(folder, dtype, device, tolerance):
 
     found = torch.cat(found)
     assert relative_error(found, wanted) < tolerance
+
+
+# ---- models of real widths, drawn on the device ----------------------------------------------------------------------
+def drawn_models(config_json: dict, seed: int, norm_jitter: float, dtypes: Sequence[str]):
+    """Draws the weights of `config_json` once on the GPU (matrices in bfloat16, vectors in 32-bit), builds one model per
+    dtype of `dtypes` from the same values (a float32 model holds the bfloat16 values widened), and returns
+    `(plain config, plain weights on the CPU in float32, {dtype: model})`.  Nothing touches a disk."""
+    from tau_rs_b200.config.registry import architecture_for
+    from tau_rs_b200.parts import DecoderModel
+    from tau_rs_b200.weights import device_dtype, random_tensors
+
+    entry = architecture_for(config_json)
+    spec = entry.build_spec(entry.parse_config(config_json))
+    device = torch.device("cuda:0")
+    models = {dtype: DecoderModel(spec, {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], device) for dtype in dtypes}
+    plain_weights = {}
+    specs = next(iter(models.values())).tensor_specs()
+    for name, tensor, tensor_spec in random_tensors(specs, seed, norm_jitter, device=device,
+                                                    dtype_of=lambda tensor_spec: device_dtype(tensor_spec, torch.bfloat16)):
+        plain_weights[name] = tensor.float().cpu()
+        for dtype, model in models.items():
+            model.assign(name, tensor.to(device_dtype(tensor_spec, model.dtype)) if len(models) > 1 else tensor)
+    for model in models.values():
+        model.finalize_weights()
+    heads = config_json["num_attention_heads"]
+    plain_config = plain_model.PlainConfig(
+        vocab_size=config_json["vocab_size"], hidden_size=config_json["hidden_size"], intermediate_size=config_json["intermediate_size"],
+        num_hidden_layers=config_json["num_hidden_layers"], num_attention_heads=heads,
+        num_key_value_heads=config_json.get("num_key_value_heads", heads), head_dim=config_json.get("head_dim", config_json["hidden_size"] // heads),
+        attention_bias=config_json.get("attention_bias", False), rms_norm_eps=config_json["rms_norm_eps"], rope_theta=config_json["rope_theta"],
+        max_position_embeddings=config_json["max_position_embeddings"], tie_word_embeddings=config_json.get("tie_word_embeddings", False))
+    return plain_config, plain_weights, models
+
+
+def plain_rows(plain_config, plain_weights, tokens: Sequence[int], rows: Sequence[int], bf16: bool) -> torch.Tensor:
+    """The plain implementation's logits of `tokens` at the positions `rows`."""
+    rounding = plain_model.bfloat16_rounding if bf16 else plain_model.no_rounding
+    return plain_model.forward_logits(plain_config, plain_weights, tokens, rounding, rows=rows)

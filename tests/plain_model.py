@@ -257,8 +257,9 @@ def decoder_block(hidden: torch.Tensor, weights: Dict[str, torch.Tensor], prefix
 
 
 def forward_logits(config: PlainConfig, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
-                   round_to: Rounding = no_rounding) -> torch.Tensor:
-    """Logits `[T, V]` at every position of one sequence.
+                   round_to: Rounding = no_rounding, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits `[T, V]` at every position of one sequence (or at the positions `rows` only: the head is the one part
+    whose cost a caller may want to bound when the vocabulary is large).
 
     Embedding, the blocks in order, the final norm and the head
     (crates/models/src/qwen3_5_common/model.rs:168-195); the head is `lm_head.weight`,
@@ -269,6 +270,8 @@ def forward_logits(config: PlainConfig, weights: Dict[str, torch.Tensor], tokens
     hidden = embedding(weights["model.embed_tokens.weight"], tokens)
     for layer in range(config.num_hidden_layers):
         hidden = decoder_block(hidden, weights, f"model.layers.{layer}", config, cos, sin, round_to)
+    if rows is not None:
+        hidden = hidden[torch.tensor(list(rows), dtype=torch.long)]
     hidden = rms_norm(hidden, weights["model.norm.weight"], config.rms_norm_eps, round_to)
     head = weights["model.embed_tokens.weight"] if config.tie_word_embeddings else weights["lm_head.weight"]
     return hidden @ head.t()
@@ -308,7 +311,7 @@ def greedy_generate(config: PlainConfig, weights: Dict[str, torch.Tensor], promp
     tokens = list(prompt)
     produced: List[int] = []
     while len(produced) < max_new_tokens:
-        logits = forward_logits(config, weights, tokens, round_to)[-1]
+        logits = forward_logits(config, weights, tokens, round_to, rows=[len(tokens) - 1])[0]
         token = greedy_token(logits.numpy())
         if token in stop_tokens:
             break

@@ -46,3 +46,24 @@ def test_refusals_are_said_before_anything_is_loaded(tmp_path):
     folder = tiny_configs.write_tiny(str(tmp_path), "A")
     with pytest.raises(Exception, match="cpu is not available"):      # the reference runs F32 there; this library has no CPU path
         cli.main(["--model", folder, "--prompt-ids", "1,2", "--device", "cpu"])
+
+
+def test_the_trace_snapshot_of_a_vector_of_logits():
+    """crates/metrics/src/logits.rs:10-60: hash over every value as little-endian 32-bit floats, 16 samples spread over
+    the vocabulary (first and last included), null for values that are not finite."""
+    import hashlib
+
+    import numpy as np
+
+    values = np.arange(100, dtype=np.float32) * 0.5
+    values[33] = np.inf
+    values[99] = np.nan
+    snapshot = cli.logit_snapshot(values, 98)
+    assert snapshot["count"] == 100 and snapshot["finite_count"] == 98 and snapshot["selected_logit"] == 49.0
+    assert snapshot["sha256_f32_le"] == hashlib.sha256(values.astype("<f4").tobytes()).hexdigest()
+    assert [sample["token_id"] for sample in snapshot["samples"]] == [i * 99 // 15 for i in range(16)]
+    assert snapshot["samples"][0]["value"] == 0.0 and snapshot["samples"][5]["value"] is None and snapshot["samples"][15]["value"] is None
+    assert cli.logit_snapshot(values, 33)["selected_logit"] is None
+    small = cli.logit_snapshot(np.array([1.5], dtype=np.float32), 0)
+    assert small["samples"] == [{"token_id": 0, "value": 1.5}] and small["count"] == 1
+    json.dumps(snapshot)
