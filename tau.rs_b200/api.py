@@ -73,9 +73,9 @@ def random_model(config_json: dict, seed: int = 0, dtype: str = "bfloat16", devi
     target = device if isinstance(device, torch.device) else resolve_device(device)
     run_dtype = _TORCH_DTYPE[canonical_dtype(dtype)]
     model = DecoderModel(spec, run_dtype, target)
-    for name, tensor, _ in random_tensors(model.tensor_specs(), seed, norm_jitter, device=target,
-                                          dtype_of=lambda tensor_spec: device_dtype(tensor_spec, run_dtype)):
-        model.assign(name, tensor)
+    # Every tensor is drawn in the run's dtype, as a folder of that storage holds it; vectors are then widened to 32-bit.
+    for name, tensor, tensor_spec in random_tensors(model.tensor_specs(), seed, norm_jitter, device=target, dtype_of=lambda _: run_dtype):
+        model.assign(name, tensor.to(device_dtype(tensor_spec, run_dtype)))
     model.finalize_weights()
     model.generation_config = GenerationConfig()
     return model

@@ -148,7 +148,7 @@ def windowed_cache_matches_whole_prompt(folder, dtype, device, tolerance):
 
 # ---- models of real widths, drawn on the device ----------------------------------------------------------------------
 def drawn_models(config_json: dict, seed: int, norm_jitter: float, dtypes: Sequence[str]):
-    """Draws the weights of `config_json` once on the GPU (matrices in bfloat16, vectors in 32-bit), builds one model per
+    """Draws the weights of `config_json` once on the GPU (every value one that bfloat16 holds), builds one model per
     dtype of `dtypes` from the same values (a float32 model holds the bfloat16 values widened), and returns
     `(plain config, plain weights on the CPU in float32, {dtype: model})`.  Nothing touches a disk."""
     from tau_rs_b200.config.registry import architecture_for
@@ -161,11 +161,10 @@ def drawn_models(config_json: dict, seed: int, norm_jitter: float, dtypes: Seque
     models = {dtype: DecoderModel(spec, {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype], device) for dtype in dtypes}
     plain_weights = {}
     specs = next(iter(models.values())).tensor_specs()
-    for name, tensor, tensor_spec in random_tensors(specs, seed, norm_jitter, device=device,
-                                                    dtype_of=lambda tensor_spec: device_dtype(tensor_spec, torch.bfloat16)):
+    for name, tensor, tensor_spec in random_tensors(specs, seed, norm_jitter, device=device, dtype_of=lambda _: torch.bfloat16):
         plain_weights[name] = tensor.float().cpu()
         for dtype, model in models.items():
-            model.assign(name, tensor.to(device_dtype(tensor_spec, model.dtype)) if len(models) > 1 else tensor)
+            model.assign(name, tensor.to(device_dtype(tensor_spec, model.dtype)))
     for model in models.values():
         model.finalize_weights()
     heads = config_json["num_attention_heads"]
