@@ -33,12 +33,24 @@ MAX_DECODE_SPLITS = 64   # decode attention merges at most this many blocks of a
 class Engine:
     """A model, its cache and the step function over both."""
 
-    def __init__(self, model, max_tokens: int, max_sequence_tokens: Optional[int] = None, max_slots: Optional[int] = None):
+    def __init__(self, model, max_tokens: int, max_sequence_tokens: Optional[int] = None, max_slots: Optional[int] = None,
+                 headroom_bytes: Optional[int] = None):
+        """`max_tokens` sizes the cache: the most tokens that live sequences hold together, each rounded up to 64.
+        On a CUDA device a cache that does not fit the free memory (less `headroom_bytes` for activations; default: the
+        larger of 2 GiB and 1/32 of the device) is refused with `CacheDoesNotFit` before anything is allocated."""
         self.model = model
         self.device = torch.device(model.device)
         limit = model.spec.max_positions
         if max_sequence_tokens is not None:
             limit = min(limit, max_sequence_tokens)
+        if self.device.type == "cuda":
+            from ..cache.budget import check_fits
+
+            free_bytes, total_bytes = torch.cuda.mem_get_info(self.device)
+            free_bytes += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)   # what torch holds unused
+            pages = -(-max_tokens // PAGE_TOKENS)
+            check_fits(model.cache_groups(), max_tokens, min(pages, max_slots) if max_slots else pages,
+                       torch.empty((), dtype=model.dtype).element_size(), free_bytes, total_bytes, headroom_bytes)
         self.cache = SequenceCache(model.cache_groups(), max_tokens, limit, model.dtype, self.device, max_slots)
         self._ring: Optional[PinnedRing] = None
         self._graphs: Dict = {}
@@ -147,6 +159,11 @@ class Engine:
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs the entries' tokens; returns 32-bit logits `[wanted places, vocab]` in the order of the
         entries and of their `want`, or None if nothing is wanted.
+
+        How long the logits stay valid: a step in which every entry brings one token and wants it (a decode step)
+        returns a buffer that belongs to the captured graph of that batch size; the next decode step of the same batch
+        size writes its logits into the same buffer.  Use them (select, copy to the host) or `clone()` them before
+        that step.  Every other step returns a tensor of its own.
 
         `device_tokens` (int32, one per entry, on the engine's device) replaces the token ids of a step in which every
         entry brings one token: the ids are taken on the device, in stream order, so a step can be started before the

@@ -161,3 +161,32 @@ def test_groups_with_and_without_a_window_side_by_side():
     cache.check()
     cache.close(slot)
     cache.check()
+
+
+def test_a_cache_that_does_not_fit_is_refused_with_what_would_fit():
+    """crates/engine/src/model_engine/tests/kv_budget.rs: pure arithmetic on a supplied memory snapshot."""
+    from tau_rs_b200.cache.budget import CacheDoesNotFit, check_fits, headroom, kv_bytes_per_token
+    from tau_rs_b200.parts.base import CacheNeed
+
+    groups = {"kv": (CacheNeed("kv", n_kv_heads=8, head_dim=128), 36)}
+    per_token = kv_bytes_per_token(groups, 2)
+    assert per_token == 147456                                         # the Qwen3-8B figure
+    gib = 1 << 30
+    assert headroom(180 * gib) == 180 * gib // 32 and headroom(16 * gib) == 2 * gib
+    assert check_fits(groups, 64 * 8192, 64, 2, 160 * gib, 180 * gib) == 64 * 8192 * per_token
+    assert check_fits(groups, 100, 2, 2, 160 * gib, 180 * gib) == 128 * per_token      # whole pages
+    with pytest.raises(CacheDoesNotFit) as refusal:
+        check_fits(groups, 64 * 8192, 64, 2, 60 * gib, 180 * gib)
+    error = refusal.value
+    assert error.asked_tokens == 64 * 8192 and error.needed_bytes == 64 * 8192 * per_token and error.free_bytes == 60 * gib
+    assert error.fitting_tokens % 64 == 0 and 0 < error.fitting_tokens < 64 * 8192
+    assert check_fits(groups, error.fitting_tokens, 64, 2, 60 * gib, 180 * gib) > 0
+    with pytest.raises(CacheDoesNotFit):
+        check_fits(groups, error.fitting_tokens + 64, 64, 2, 60 * gib, 180 * gib)
+    with pytest.raises(CacheDoesNotFit) as nothing:
+        check_fits(groups, 64, 1, 2, 1 * gib, 180 * gib)
+    assert nothing.value.fitting_tokens == 0 and "at most 0 tokens" in str(nothing.value)
+    with pytest.raises(ValueError):
+        check_fits(groups, 64, 1, 2, 200 * gib, 180 * gib)
+    state = {"kv": groups["kv"], "s": (CacheNeed("state", state_shape=(4, 16), state_dtype=torch.float32), 3)}
+    assert check_fits(state, 64, 5, 2, 160 * gib, 180 * gib, headroom_bytes=0) == 64 * per_token + 5 * 3 * 4 * 16 * 4

@@ -334,3 +334,19 @@ def test_a_long_context_at_the_width_of_a_real_model(tmp_path, length, config):
     engine.close_sequence(slot)
     engine.cache.check()
     assert kernels.attention_prefill_tc_status(config["head_dim"]) == 0 and kernels.gemm_tc_status() == 0
+
+
+def test_a_cache_larger_than_the_device_is_refused_before_anything_is_allocated(folders):
+    """crates/engine/src/model_engine/kv_budget.rs:17-56: a named error, not an out-of-memory failure of the allocator."""
+    from tau_rs_b200 import CacheDoesNotFit, Engine, load_model
+
+    model = load_model(folders[("A", "float32")], "float32", "gpu")
+    free, total = torch.cuda.mem_get_info()
+    before = torch.cuda.memory_allocated()
+    per_token = 2 * 2 * 2 * 16 * 4          # keys and values, 2 layers, 2 KV heads of 16, 32-bit
+    with pytest.raises(CacheDoesNotFit) as refusal:
+        Engine(model, max_tokens=(total // per_token) * 2)
+    assert torch.cuda.memory_allocated() == before
+    assert 0 < refusal.value.fitting_tokens < total // per_token and "fits" in str(refusal.value)
+    engine = Engine(model, max_tokens=4096, headroom_bytes=0)
+    assert engine.capacity_tokens == 4096
