@@ -100,7 +100,7 @@ def _attention_shapes(heads: int, kv_heads: int, dim: int, capacity: int) -> Non
 
 
 def decode_attention_prepare(query_gate, key, value, query_weight, key_weight, cos, sin, query_out, cached_key, cached_value, meta,
-                             heads: int, kv_heads: int, dim: int, capacity: int, rotary_dim: int, eps: float) -> None:
+                             heads: int, kv_heads: int, dim: int, capacity: int, rotary_dim: int, eps: float, position: int = None) -> None:
     """`tau_launch_decode_attention_prepare` (decode_attention.cu:307-345) with 32-bit rotation tables and the
     position-major cache: one token at position `meta[1]`; `query_gate` `[heads, 2 dim]` (the query, then a gate that is
     not read), `key`/`value` `[kv_heads, dim]`, norm weights `[dim]` scaling by `1 + w`, tables `[positions, rotary_dim / 2]`
@@ -113,7 +113,7 @@ def decode_attention_prepare(query_gate, key, value, query_weight, key_weight, c
     assert query_weight.numel() == key_weight.numel() == dim and cached_key.shape == cached_value.shape == (kv_heads, capacity, dim)
     assert 0 < rotary_dim <= dim and rotary_dim % 2 == 0 and cos.dtype == sin.dtype == torch.float32 and cos.shape == sin.shape
     assert meta.dtype == torch.int32 and meta.numel() == 2
-    position = int(meta[1])
+    position = int(meta[1]) if position is None else position     # a caller that times the launch names the position itself
     assert 0 <= position < capacity and position < cos.shape[0] and cos.shape[1] == rotary_dim // 2 and eps > 0
     _ok(_library("decode_attention").tau_launch_decode_attention_prepare(
         _p(query_gate), _p(key), _p(value), _p(query_weight), _p(key_weight), _p(cos), _p(sin), _p(query_out), _p(cached_key), _p(cached_value),
@@ -122,7 +122,7 @@ def decode_attention_prepare(query_gate, key, value, query_weight, key_weight, c
 
 
 def decode_attention(query, cached_key, cached_value, out, meta, workspace, heads: int, kv_heads: int, dim: int, capacity: int,
-                     block_size: int) -> None:
+                     block_size: int, position: int = None) -> None:
     """`tau_launch_decode_attention` (decode_attention.cu:348-365) with 32-bit products: one query token at position
     `meta[1]` over the positions `0 .. meta[1]` of the caches; the context is cut into tiles of `block_size` positions
     whose records `(max, sum, context)` a second kernel merges.  `workspace`: `heads * ceil(capacity / block_size) *
@@ -134,7 +134,7 @@ def decode_attention(query, cached_key, cached_value, out, meta, workspace, head
     assert splits <= 256 and workspace.dtype == torch.float32 and workspace.numel() >= heads * splits * (dim + 2)
     assert query.numel() == out.numel() == heads * dim and query.dtype == out.dtype == cached_key.dtype == cached_value.dtype == torch.bfloat16
     assert cached_key.shape == cached_value.shape == (kv_heads, capacity, dim) and meta.dtype == torch.int32 and meta.numel() == 2
-    assert 0 <= int(meta[1]) < capacity
+    assert 0 <= (int(meta[1]) if position is None else position) < capacity
     _ok(_library("decode_attention").tau_launch_decode_attention(
         _p(query), _p(cached_key), _p(cached_value), _p(out), _p(meta), _p(workspace), ctypes.c_int(heads), ctypes.c_int(kv_heads),
         ctypes.c_int(dim), ctypes.c_int(capacity), ctypes.c_int(0), ctypes.c_int(block_size), ctypes.c_int(0), _stream()), "decode attention")

@@ -54,6 +54,8 @@ def build_parser() -> argparse.ArgumentParser:
     logging = parser.add_argument_group("Logging options")
     logging.add_argument("--metrics", action="store_true", help="Log live decode t/s to stderr. [default: off] Every ~5s during generation and at completion.")
     logging.add_argument("--tracing", action="store_true", help="Log numerical traces (token ids, logit checksums) to stdout. [default: off]")
+    logging.add_argument("--hbm-gbs", type=float, default=None, metavar="GB/s",
+                         help="The device's measured copy bandwidth; with --metrics the report then carries the decode steps' fraction of that roofline.")
     logging.add_argument("--vram-metrics", action="store_true", help="Sample process VRAM; log peak to stderr. [default: off] Independent of --metrics and --tracing.")
     return parser
 
@@ -112,6 +114,9 @@ class _Tracer:
         tokens = self.select(logits, request_ids, token_indices)
         host = logits.float().cpu().numpy()
         end = time.perf_counter()
+        from .csrc import kernels
+
+        by_class = kernels.take_timing()      # milliseconds per kernel class since the select before (empty unless timing is on)
         for row, (request, index, token) in enumerate(zip(request_ids, token_indices, tokens)):
             prompt_tokens = len(self.prompts[request])
             self.steps.append({
@@ -120,6 +125,7 @@ class _Tracer:
                 "token_id": int(token), "is_eos": int(token) in self.stop,
                 "start_us": round((begin - self.started) * 1e6, 1), "duration_us": round((end - begin) * 1e6, 1),
                 "logits": logit_snapshot(host[row], int(token)),
+                **({"kernel_class_ms": by_class} if by_class and row == 0 else {}),
             })
         self.boundary = time.perf_counter()
         return tokens
@@ -170,7 +176,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     engine.attention_block_size = args.attention_block_size
     select = Sampler(SamplingParams(args.temperature, args.seed))   # the object, not its method: the loop then decodes one step ahead
     tracer = _Tracer(select, prompts, stop) if args.tracing else None
-    metrics = GenerationMetrics()
+    if tracer:
+        # A traced run times the kernel classes of every step with CUDA events (crates/metrics/src/timing.rs:83-183 does so
+        # for its decode phases), which needs the launches themselves: no replayed graph.
+        engine.use_graphs = False
+        kernels.start_timing()
+    metrics = GenerationMetrics(peak_gb_per_second=args.hbm_gbs)
     if args.metrics:   # live: every ~5 s during generation and at completion
         metrics.log_interval_s = 5.0
         metrics.sink = lambda record: print("inference_metrics " + json.dumps(record), file=sys.stderr, flush=True)

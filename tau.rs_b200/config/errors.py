@@ -43,3 +43,8 @@ class WeightError(ModelLoadError):
         for name, found in self.wrong_dtype:
             lines.append(f"  unsupported storage dtype: {name} is {found}")
         super().__init__("\n".join(lines))
+
+
+class AllLogitsNaN(RuntimeError):
+    """Every logit of a live request's row is NaN: there is nothing to choose from
+    (crates/engine/src/generation.rs:81-95 raises the same)."""

@@ -219,7 +219,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                             const __grid_constant__ CUtensorMap v_map, bf16* __restrict__ out, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_start, const int* __restrict__ page_rows, int page_stride, int n_seqs,
                             int n_heads, int n_kv_heads, float scale, int window) {
-    grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     uint8_t* tiles = shared_raw;                                   // the swizzled tiles need 1,024-byte alignment
     uint8_t* q_tile = tiles;                                       // kHalves slices of [128 rows x 128 bytes]
@@ -262,6 +261,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     __syncthreads();
     tensor_fence_after_sync();
     const uint32_t tensor_base = shared->tensor_memory_base;
+    // The next kernel's blocks may start only now that this block holds its tensor memory: had one of them taken the
+    // columns first, this block's allocation would wait for a kernel that waits for this one.
+    grid_dependents_launch();
     grid_dependency_wait();
 
     // Which sequence and which 128-row tile of it?  Blocks are numbered sequence by sequence, last tiles first.

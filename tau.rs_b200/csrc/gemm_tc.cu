@@ -183,7 +183,6 @@ __global__ void __launch_bounds__(kThreads, BN <= 128 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
                const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages,
                int splits, float* __restrict__ workspace, int* __restrict__ tickets, int clustered) {
-    grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
@@ -219,6 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
     __syncthreads();
     tensor_fence_after_sync();
     const uint32_t tensor_base = shared->tensor_memory_base;
+    // Only now may the next kernel's blocks start beside this one: a block of it that took tensor memory before this block
+    // had its own would make this block's allocation wait for a kernel that in turn waits for this one.
+    grid_dependents_launch();
     // Barriers and tensor memory were set up while the previous kernel was finishing.  Each role waits for that kernel
     // only before it touches what that kernel may write or read: the inputs (producer) and the output (epilogue).
 
@@ -527,7 +529,6 @@ template <typename TOut, bool Gated>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
                     const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
-    grid_dependents_launch();
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
@@ -564,6 +565,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid
     cluster_sync_all();   // both blocks' barriers exist before either signals the other's
     tensor_fence_after_sync();
     const uint32_t tensor_base = shared->tensor_memory_base;
+    grid_dependents_launch();   // after this pair holds its tensor memory (see gemm_tc_kernel)
 
     if (warp == 0) {
         // ---- producer (both blocks): this block's weight rows and its half of the tokens ----------------------

@@ -63,9 +63,52 @@ def count_replay(kernels_in_graph: int) -> None:
     _replayed += kernels_in_graph
 
 
+# Kernel classes for the timing of a step (crates/metrics/src/timing.rs:83-183 times the phases of a decode step with
+# CUDA events): what each launch is booked under.
+_CLASS_OF = {
+    "embedding": "embedding", "rms_norm": "norm", "add_rms_norm": "norm", "silu_mul": "activation", "gemm_simt": "product",
+    "gemm_skinny": "product", "gemm_tc": "product", "attention_prepare": "attention", "attention": "attention",
+    "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
+    "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
+}
+_timing = None     # while timing: [last event, [(class, event after the launch), ...]]
+
+
+def start_timing() -> None:
+    """From now on an event follows every launch of this library on the current stream; `take_timing` reads them.
+    Meant for steps that run outside a captured graph."""
+    global _timing
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    _timing = [first, []]
+
+
+def take_timing(stop: bool = False) -> dict:
+    """Milliseconds per kernel class since `start_timing` or the last `take_timing` (waits for the stream).  The time of
+    a launch runs from the end of the launch before it, so gaps between kernels are booked to the kernel that follows."""
+    global _timing
+    if _timing is None:
+        return {}
+    first, marks = _timing
+    totals = {}
+    if marks:
+        marks[-1][1].synchronize()
+        previous = first
+        for name, event in marks:
+            totals[name] = totals.get(name, 0.0) + previous.elapsed_time(event)
+            previous = event
+        first = marks[-1][1]
+    _timing = None if stop else [first, []]
+    return {name: round(value, 4) for name, value in totals.items()}
+
+
 def _check(status: int, what: str, kernels_launched: int = 1) -> None:
     global _launches
     _launches += kernels_launched
+    if _timing is not None and status == 0 and not torch.cuda.is_current_stream_capturing():
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        _timing[1].append((_CLASS_OF.get(what, "other"), event))
     if status != 0:
         library = build.load_library("elementwise.cu")
         library.tau_error_string.restype = ctypes.c_char_p

@@ -30,6 +30,7 @@ from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
 from ..cache.sequence_cache import PAGE_TOKENS, pages_for
+from ..config.errors import AllLogitsNaN
 from .batch import StepEntry
 
 
@@ -48,7 +49,11 @@ class GenerationMetrics:
 
     With `log_interval_s` and `sink`, a record with `status: "running"` goes to `sink` at a token boundary whenever
     that many seconds have passed since the last one (serving.rs:56-58,92-95,160-165: every 5 s there, no thread of
-    its own); `interval_decode_tokens_per_second` is the rate of the decode work since the record before (:46-47)."""
+    its own); `interval_decode_tokens_per_second` is the rate of the decode work since the record before (:46-47).
+
+    Beyond the reference's fields: where the backend says how many bytes a decode step has to read (every weight once and
+    the cache of the live requests), `decode_gb_per_second` is that over the decode time, and with `peak_gb_per_second`
+    (the device's measured copy bandwidth) `fraction_of_roofline` is their ratio."""
 
     prompt_tokens: int = 0
     generated_tokens: int = 0
@@ -58,6 +63,8 @@ class GenerationMetrics:
     prefill_steps: int = 0
     decode_steps: int = 0
     batches: int = 0
+    decode_bytes: int = 0
+    peak_gb_per_second: Optional[float] = None
     log_interval_s: Optional[float] = None
     sink: Optional[Callable[[dict], None]] = None
     _started: float = field(default_factory=time.perf_counter, repr=False)
@@ -87,6 +94,10 @@ class GenerationMetrics:
         return self.decode_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
 
     @property
+    def decode_gb_per_second(self) -> Optional[float]:
+        return self.decode_bytes / (self.decode_ms * 1e6) if self.decode_bytes and self.decode_ms > 0 else None
+
+    @property
     def prefill_tokens_per_second(self) -> float:
         return self.prompt_tokens / (self.prefill_ms / 1e3) if self.prefill_ms > 0 else 0.0
 
@@ -98,6 +109,9 @@ class GenerationMetrics:
             "decode_tokens_per_second": round(self.decode_tokens_per_second, 2),
             "prefill_tokens_per_second": round(self.prefill_tokens_per_second, 2),
             "prefill_steps": self.prefill_steps, "decode_steps": self.decode_steps, "batches": self.batches,
+            "decode_gb_per_second": self.decode_gb_per_second and round(self.decode_gb_per_second, 1),
+            "fraction_of_roofline": (round(self.decode_gb_per_second / self.peak_gb_per_second, 4)
+                                     if self.decode_gb_per_second and self.peak_gb_per_second else None),
         }
 
 
@@ -190,6 +204,8 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
             live.remove(item)
 
         def accept(item: _Live, token: int) -> None:
+            if token < 0:   # the selector found only NaN in this request's row
+                raise AllLogitsNaN(f"request {item.request}: model logits are all NaN")
             if token in stop:
                 finish(item, "stop")
                 return
@@ -227,9 +243,10 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
             accept(item, first_tokens[item.request])
 
         # Decode: one token for every request that is still going.
+        step_bytes = getattr(backend, "bytes_read_by_a_decode_step", lambda: 0)
         launch, collect = getattr(select, "launch", None), getattr(select, "collect", None)
         if launch is not None and collect is not None and getattr(backend, "accepts_device_tokens", False):
-            _decode_ahead(backend, live, launch, collect, stop, accept, metrics)
+            _decode_ahead(backend, live, launch, collect, stop, accept, metrics, step_bytes)
         while live:
             started = time.perf_counter()
             entries = [StepEntry(item.slot, [item.produced[-1]], [0]) for item in live]
@@ -237,6 +254,7 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
             tokens = select(logits, [item.request for item in live], [len(item.produced) for item in live])
             metrics.decode_ms += (time.perf_counter() - started) * 1e3
             metrics.decode_steps += 1
+            metrics.decode_bytes += step_bytes()
             for item, token in zip(list(live), tokens):
                 if token not in stop:
                     metrics.decode_tokens += 1
@@ -247,7 +265,7 @@ def _run_batch(backend, requests, prompts, limits, select, stop, chunk, metrics,
             backend.close_sequence(item.slot)
 
 
-def _decode_ahead(backend, live, launch, collect, stop, accept, metrics) -> None:
+def _decode_ahead(backend, live, launch, collect, stop, accept, metrics, step_bytes=lambda: 0) -> None:
     """The decode loop, one step ahead of the host; returns with `live` empty."""
     if not live:
         return
@@ -257,6 +275,7 @@ def _decode_ahead(backend, live, launch, collect, stop, accept, metrics) -> None
     logits = backend.step([StepEntry(item.slot, [item.produced[-1]], [0]) for item in items])
     pending = launch(logits, [item.request for item in items], [len(item.produced) for item in items])
     metrics.decode_steps += 1
+    metrics.decode_bytes += step_bytes()
     while True:
         # Who goes on after the token that is on its way?  Not those whose limit it reaches; the others do, unless it
         # turns out to be a stop token, which is known only after their next step has been started.
@@ -269,6 +288,7 @@ def _decode_ahead(backend, live, launch, collect, stop, accept, metrics) -> None
             logits = backend.step([StepEntry(item.slot, [0], [0]) for item in next_items], device_tokens=tokens_on_device)
             following = launch(logits, [item.request for item in next_items], [len(item.produced) + 1 for item in next_items])
             metrics.decode_steps += 1
+            metrics.decode_bytes += step_bytes()
         tokens = collect(pending)
         for item, token in zip(items, tokens):
             if item not in live:      # stopped one step ago; this token was computed for nothing

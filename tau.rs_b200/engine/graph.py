@@ -7,6 +7,13 @@ and one wanted place each); everything that changes between steps (tokens, posit
 page rows, lengths) lies in the metadata buffer at a fixed address, and kernels take no
 host value that depends on the sequences' lengths except the number of context splits,
 which is part of the graph's key.
+
+All graphs of an engine are captured into one memory pool and warmed up on one side stream, and the
+least recently used ones are dropped beyond `MAX_GRAPHS`, so a batch that shrinks request by request
+does not leave a private pool of activations and logits behind for every size it went through.
+A mixer that updates per-sequence state in place would see its state advanced twice, by the warm-up
+run and by the first replay; the state of the step's sequences is therefore put back after the
+warm-up (the reference snapshots such state around its warm-up the same way, model/graph.rs:183-211).
 """
 from __future__ import annotations
 
@@ -17,6 +24,8 @@ import torch
 
 from ..csrc import kernels
 from .batch import StepEntry, StepLayout, step_views
+
+MAX_GRAPHS = 96   # per engine; a graph of a Qwen3-8B step holds a few MB of activations and its logits
 
 
 class _DecodeGraph:
@@ -64,9 +73,12 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
     if splits is None:
         splits = engine._split_choice[bucket] = engine.decode_splits(len(entries), max_len)
     key = (len(entries), splits)
-    state = engine._graphs.get(key)
+    state = engine._graphs.pop(key, None)
     if state is None:
-        state = engine._graphs[key] = _DecodeGraph(engine, len(entries), splits)
+        state = _DecodeGraph(engine, len(entries), splits)
+        while len(engine._graphs) >= MAX_GRAPHS:
+            engine._graphs.pop(next(iter(engine._graphs)))     # the least recently used: a dict keeps its order
+    engine._graphs[key] = state                                 # (re-)inserted as the most recent
     engine.last_step_ints = state.layout.total
     staged, ticket = engine.ring(state.layout.total).acquire(state.layout.total)
     state.fill(staged, entries, starts, engine.cache)
@@ -77,14 +89,21 @@ def run_decode_graph(engine, entries: Sequence[StepEntry], starts: Sequence[int]
     context.max_len = max_len
     if state.graph is None:
         # Warm-up outside capture: compiles and loads every kernel, sizes torch's pools.
-        stream = torch.cuda.Stream()
+        if engine._graph_stream is None:
+            engine._graph_stream = torch.cuda.Stream()
+            engine._graph_pool = torch.cuda.graph_pool_handle()
+        stream = engine._graph_stream
+        slots = [entry.slot for entry in entries]
+        kept = {name: group.state[:, slots].clone() for name, group in engine.cache.states.items()}
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             engine.model.forward(context, engine.cache)
         torch.cuda.current_stream().wait_stream(stream)
+        for name, group in engine.cache.states.items():        # the warm-up advanced the state; the replay below is the step
+            group.state[:, slots] = kept[name]
         graph = torch.cuda.CUDAGraph()
         before = kernels.launch_count()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, pool=engine._graph_pool, stream=stream):
             state.logits = engine.model.forward(context, engine.cache)
         state.launches = kernels.launch_count() - before
         state.graph = graph

@@ -54,10 +54,13 @@ class Engine:
         self.cache = SequenceCache(model.cache_groups(), max_tokens, limit, model.dtype, self.device, max_slots)
         self._ring: Optional[PinnedRing] = None
         self._graphs: Dict = {}
+        self._graph_stream = None
+        self._weight_bytes = None
+        self._graph_pool = None
         self._split_choice: Dict = {}
         self.last_step_ints = 0     # size of the last step's metadata (int32 words copied to the device)
-        # A captured step runs more than once while it is captured; state that a mixer updates in place forbids that.
-        self.use_graphs = self.device.type == "cuda" and not self.cache.states
+        # Decode steps replay a captured graph unless a part of the model says that it cannot be captured.
+        self.use_graphs = self.device.type == "cuda" and all(getattr(block, "capturable", True) for block in model.blocks)
         # Context tokens per block of decode attention (`--attention-block-size`, crates/server/src/args.rs: "context tokens
         # per prepared decode attention tile"); None: chosen from the batch and the context by `DecoderModel.decode_splits`.
         self.attention_block_size: Optional[int] = None
@@ -93,6 +96,12 @@ class Engine:
     @property
     def max_sequence_tokens(self) -> int:
         return self.cache.max_sequence_tokens
+
+    def bytes_read_by_a_decode_step(self) -> int:
+        """Every weight once, and the cached keys and values of the live sequences: what a decode step of all of them reads."""
+        if self._weight_bytes is None:
+            self._weight_bytes = self.model.weight_bytes()
+        return self._weight_bytes + self.cache.live_bytes()
 
     # ---- the step ----------------------------------------------------------------
     accepts_device_tokens = True   # `step(entries, device_tokens=...)`

@@ -40,6 +40,10 @@ class Attention(Mixer):
         if spec.qk_norm is not None:
             if spec.qk_norm.width != spec.head_dim:
                 raise ValueError("the q/k norm runs over head_dim")
+            # The prepare and decode kernels compute this norm themselves, from its weight and eps: `x * rsqrt(mean(x^2) + eps) * w`.
+            # A norm part of another kind (a centred weight, a bias) would be computed wrongly without a word, so it is refused.
+            if spec.qk_norm.kind != "rms_norm":
+                raise ValueError(f"the attention kernels compute the q/k norm as rms_norm; a q/k norm of kind {spec.qk_norm.kind!r} is not served")
             self.q_norm = build("norm", spec.qk_norm, name=f"{prefix}.q_norm.weight", dtype=dtype, device=device)
             self.k_norm = build("norm", spec.qk_norm, name=f"{prefix}.k_norm.weight", dtype=dtype, device=device)
         self.position = None

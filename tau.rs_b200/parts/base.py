@@ -52,7 +52,17 @@ class Mixer(Part):
     `StateLayerView`), or None if `cache_need()` is None.
     """
 
+    # False: a decode step through this mixer cannot be captured in a CUDA graph (its `forward` reads device values on the
+    # host, say); an engine whose model has such a part runs its decode steps launch by launch.
+    capturable = True
+
     def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def decode_blocks(self) -> Optional[int]:
+        """Blocks that the mixer's decode kernel launches per sequence and context split, where the mixer splits the
+        context of a decode step at all (None: it does not).  The number of splits is chosen so that all blocks of a step
+        are resident at once, and it is part of a captured graph's key."""
         return None
 
     def forward(self, hidden, step, cache, writes_cache: bool):
@@ -61,6 +71,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """`forward(hidden, step)`: `[tokens, hidden] -> [tokens, hidden]`, token by token."""
+
+    capturable = True   # as for a mixer
 
     def forward(self, hidden, step):
         raise NotImplementedError
@@ -89,7 +101,13 @@ class Block(Part):
     `forward(residual, branch, step, cache, writes_cache) -> (residual, branch)`.
     """
 
+    capturable = True   # False if a part of the block is not
+
     def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def decode_blocks(self) -> Optional[int]:
+        """The mixer's answer (see `Mixer.decode_blocks`)."""
         return None
 
     def forward(self, residual, branch, step, cache, writes_cache: bool):

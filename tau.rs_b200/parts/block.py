@@ -16,22 +16,28 @@ from .registry import build, register_block
 class PreNormBlock(Block):
     mixer_name = "self_attn"
     feed_forward_name = "mlp"
+    mixer_norm_name = "input_layernorm"
+    feed_forward_norm_name = "post_attention_layernorm"
 
     def __init__(self, spec, dtype, device):
         self.spec = spec
         prefix = spec.prefix
-        self.mixer_norm = build("norm", spec.mixer_norm, name=f"{prefix}.input_layernorm.weight", dtype=dtype, device=device)
+        self.mixer_norm = build("norm", spec.mixer_norm, name=f"{prefix}.{self.mixer_norm_name}.weight", dtype=dtype, device=device)
         self.mixer = build("mixer", spec.mixer, prefix=f"{prefix}.{self.mixer_name}", dtype=dtype, device=device)
         self.feed_forward_norm = build(
-            "norm", spec.feed_forward_norm, name=f"{prefix}.post_attention_layernorm.weight", dtype=dtype, device=device
+            "norm", spec.feed_forward_norm, name=f"{prefix}.{self.feed_forward_norm_name}.weight", dtype=dtype, device=device
         )
         self.feed_forward = build(
             "feed_forward", spec.feed_forward, prefix=f"{prefix}.{self.feed_forward_name}", dtype=dtype, device=device
         )
         self._children = (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        self.capturable = all(getattr(part, "capturable", True) for part in self._children)
 
     def cache_need(self):
         return self.mixer.cache_need()
+
+    def decode_blocks(self):
+        return self.mixer.decode_blocks()
 
     def tensor_specs(self):
         specs = {}

@@ -113,9 +113,8 @@ class DecoderModel:
 
     def decode_splits(self, n_seqs: int, max_len: int) -> int:
         """Context splits for a decode step of `n_seqs` sequences (part of a captured graph's key)."""
-        blocks = [block.mixer.decode_blocks() for block in self.blocks
-                  if hasattr(block, "mixer") and hasattr(block.mixer, "decode_blocks")]
-        return kernels.decode_splits(n_seqs, max_len, min(blocks) if blocks else 1)
+        blocks = [count for count in (block.decode_blocks() for block in self.blocks) if count]
+        return kernels.decode_splits(n_seqs, max_len, min(blocks)) if blocks else 1
 
     # ---- forward -----------------------------------------------------------------
     def forward(self, step, cache) -> Optional[torch.Tensor]:

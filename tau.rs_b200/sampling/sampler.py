@@ -17,6 +17,7 @@ from typing import List, Sequence
 
 import torch
 
+from ..config.errors import AllLogitsNaN
 from ..csrc import kernels
 
 
@@ -30,8 +31,7 @@ class SamplingParams:
             raise ValueError("temperature must be zero (greedy) or positive")
 
 
-class AllLogitsNaN(RuntimeError):
-    pass
+NO_TOKEN = -1   # what `collect` gives for a row with nothing to choose from
 
 
 class Pending:
@@ -81,16 +81,18 @@ class Sampler:
         return Pending(result, host, done)
 
     def collect(self, pending: Pending) -> List[int]:
-        """Blocks until the tokens of `pending` are on the host."""
+        """Blocks until the tokens of `pending` are on the host.  A row that held only NaN gives `NO_TOKEN`: whether that
+        is an error is for the caller to say, who knows whether the row's request is still going."""
         if pending.done is not None:
             pending.done.synchronize()
         tokens, valid = pending.host.tolist()
-        if not all(valid):
-            raise AllLogitsNaN("model logits are all NaN")
-        return tokens
+        return [token if ok else NO_TOKEN for token, ok in zip(tokens, valid)]
 
     def select(self, logits: torch.Tensor, request_ids: Sequence[int], token_indices: Sequence[int]) -> List[int]:
         """One token for each row of `logits` `[rows, vocab]`; blocks until the tokens are on the host."""
-        return self.collect(self.launch(logits, request_ids, token_indices))
+        tokens = self.collect(self.launch(logits, request_ids, token_indices))
+        if NO_TOKEN in tokens:
+            raise AllLogitsNaN("model logits are all NaN")
+        return tokens
 
     __call__ = select

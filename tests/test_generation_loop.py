@@ -340,3 +340,31 @@ def test_decode_split_rule_stays_within_what_the_kernel_and_the_machine_take():
                     assert decode_splits(n_seqs, low, kv_blocks, sms) == splits == decode_splits(n_seqs, bucket, kv_blocks, sms)
     assert decode_splits(8, 2049, 8, 148) == 8 and decode_splits(1, 2049, 8, 148) == 16 and decode_splits(64, 2049, 8, 148) == 1
     assert decode_splits(8, 2049, 8, 132) == 8 and decode_splits(8, 2049, 8, 74) == 4
+
+
+def test_a_row_of_nan_is_an_error_only_for_a_request_that_is_still_going():
+    """One step ahead of the host, a request that stopped has one more token computed for nothing; if that row holds
+    nothing to choose from (the selector's -1), nobody asked for it.  The same answer for a live request is the
+    reference's "model logits are all NaN" (crates/engine/src/generation.rs:81-95)."""
+    from tau_rs_b200.config.errors import AllLogitsNaN
+
+    class NaNAfterStop(TwoHalves):
+        """Gives -1 for request 0 from its token index 3 on."""
+
+        def launch(self, rows, request_ids, token_indices):
+            rows = [-1 if request == 0 and index >= self.first_bad else row for row, request, index in zip(rows, request_ids, token_indices)]
+            return super().launch(rows, request_ids, token_indices)
+
+    prompts = [[7, 1, 1], [20, 2]]
+    free = [expected_tokens(prompt, 6) for prompt in prompts]
+    selector = NaNAfterStop()
+    selector.first_bad = 3
+    results = generate_tokens(AheadBackend(), prompts, 6, selector, stop_tokens=[free[0][2]])
+    assert results[0].tokens == free[0][:2] and results[0].finish_reason == "stop"    # its row of token index 3 was computed and dropped
+    assert results[1].tokens == free[1]
+    selector = NaNAfterStop()
+    selector.first_bad = 2
+    backend = AheadBackend()
+    with pytest.raises(AllLogitsNaN):
+        generate_tokens(backend, prompts, 6, selector, stop_tokens=[free[0][4]])
+    assert backend.open == set()

@@ -162,6 +162,11 @@ class DecayMixer(Mixer):
 
     def forward(self, hidden, step, cache, writes_cache):
         projected = hidden.float() @ self.weight.float().t()
+        if step.all_single:   # one token per sequence: everything stays on the device, so the step can be captured in a graph
+            slots = step.seq_slot.long()
+            state = cache.state.index_select(0, slots) * self.spec.decay + projected
+            cache.state.index_copy_(0, slots, state)
+            return state.to(hidden.dtype)
         out = torch.empty_like(projected)
         bounds, slots = step.cu_seqlens.cpu().tolist(), step.seq_slot.cpu().tolist()
         for index, slot in enumerate(slots):
@@ -211,7 +216,13 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(toy_architecture
     assert set(model.cache_groups()) == {"decay", "keys"}
     assert model.cache_groups()["decay"][1] == 2 and model.cache_groups()["keys"][1] == 1
     engine = Engine(model, 64 * 6)
-    assert not engine.use_graphs                      # state that is updated in place is never replayed
+    # Decode steps are captured: the warm-up run before a capture advances the state once, and it is put back before the replay.
+    assert engine.use_graphs
+    DecayMixer.capturable = False
+    try:
+        assert not Engine(load_model(folder, "float32", DEVICE), 64).use_graphs      # a part that cannot be captured says so
+    finally:
+        DecayMixer.capturable = True
     rng = np.random.default_rng(0)
     requests = [rng.integers(0, 97, size=length).tolist() for length in (70, 9, 33)]
 

@@ -163,14 +163,17 @@ def test_the_command_line_generates_the_plain_tokens(folders, tmp_path):
     records, _, _ = run_cli(base)
     assert [record["tokens"] for record in records] == wanted
     assert [record["finish_reason"] for record in records] == ["length" if len(tokens) == 7 else "stop" for tokens in wanted]
-    records, trace, errors = run_cli(base + ["--cuda-graph", "none", "--tracing", "--metrics", "--vram-metrics"])
+    records, trace, errors = run_cli(base + ["--cuda-graph", "none", "--tracing", "--metrics", "--vram-metrics", "--hbm-gbs", "6537.3"])
     assert [record["tokens"] for record in records] == wanted
-    assert "inference_metrics " in errors
+    report = [json.loads(line[len("inference_metrics "):]) for line in errors.splitlines() if line.startswith("inference_metrics ")][-1]
+    assert report["status"] == "ok" and report["decode_tokens"] > 0 and report["decode_gb_per_second"] > 0
+    assert 0 < report["fraction_of_roofline"] < 1
     (trace,) = trace
     assert trace["generated"] == wanted and trace["prompts"] == prompts
     first = [step for step in trace["steps"] if step["request"] == 0 and step["phase"] == "prefill"][0]
     assert first["cache_offset"] == 0 and first["input_tokens"] == 9 and first["token_id"] == wanted[0][0] and first["is_eos"] is False
     assert len(first["logits"]["samples"]) == 16 and first["logits"]["count"] == 256 and first["duration_us"] > 0
+    assert set(first["kernel_class_ms"]) >= {"embedding", "norm", "product", "attention"} and first["kernel_class_ms"]["product"] > 0
     decode = [step for step in trace["steps"] if step["request"] == 0 and step["phase"] == "decode"]
     assert [step["cache_offset"] for step in decode] == [9 + index for index in range(len(decode))]
     out = tmp_path / "replay"
