@@ -488,14 +488,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_cons
 // ---- pairs of SMs on one tile ------------------------------------------------------------------------------
 // For many tokens the product is bound by the tensor cores, and a 128 x 256 tile per SM spends as much shared-memory
 // bandwidth on filling and reading its operands as the products can use.  Two blocks of a cluster therefore share a
-// 256 (features) x 256 (tokens) tile: each brings its own 128 weight rows and half of the tokens, one thread of the
-// first block issues tcgen05.mma.cta_group::2, which reads the token halves of both blocks, and each block's tensor
-// memory receives its 128 features x 256 tokens.  Per product a block now fills 32 KB of shared memory, not 48 KB.
+// 256 (tokens) x 256 (features) tile: each brings 128 of the tokens and half of the weight rows, one thread of the first
+// block issues tcgen05.mma.cta_group::2, which reads the weight halves of both blocks, and each block's tensor memory
+// receives its 128 tokens x 256 features.  Per product a block fills 32 KB of shared memory, not 48 KB.
+//
+// Here the tokens are the rows of the product (lanes of tensor memory) and the features its columns, so an epilogue
+// thread owns one token and reads runs of neighbouring features: it stores 16 bytes at a time where the output's rows
+// allow it, and the gate and up values of a gated product (groups of 8 and 8 features) meet inside one thread.
+//
+// Pair `p` takes the tiles `p, p + pairs, ...`: at any time the pairs work on neighbouring tiles at the same depth of
+// K, so a block of the weight or of the input is fetched from memory once and hit in L2 by the others within
+// microseconds.  (Sharing out the last, partly filled wave in quarter tiles of 64 features was measured and is not
+// done: copies of 32 weight rows and products of 64 to 192 features ran so much slower that the products of a
+// 2,048-token prefill layer took 655 us against 551 us.)
 //
 // The first block's `full` barriers count the bytes of both blocks' copies (the peer's TMA copies signal them across
 // the cluster); tcgen05.commit signals `empty` and `accumulator_full` in both blocks; the epilogue warps of both
 // blocks release an accumulator at the first block's barrier.  All waits are bounded as above.  No copy is multicast.
-constexpr int kPairTokens = 256, kPairHalf = 128;
+constexpr int kPairTokens = 256, kPairHalf = 128, kPairFeatures = 256;
 
 __device__ __forceinline__ void barrier_arrive_cluster(uint32_t cluster_barrier) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_barrier) : "memory");
@@ -525,20 +535,42 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t* barrier) {
                  : "memory");
 }
 
+// 32 consecutive columns of this thread's lane; the caller waits (`tensor_load_wait`) before it uses them.
+__device__ __forceinline__ void tensor_load_32(uint32_t address, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(address));
+}
+
+__device__ __forceinline__ void tensor_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_pair(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+// `vector_stores`: the output's rows start on 16 bytes and N is a multiple of 8 (16 where gated), so 16-byte stores of
+// whole groups of features are safe; otherwise every value is stored on its own.
 template <typename TOut, bool Gated>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap input_map,
-                    const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages) {
+                    const float* __restrict__ bias, TOut* __restrict__ out, int M, int N, int K, long long out_stride, int stages,
+                    int vector_stores) {
     extern __shared__ uint8_t shared_raw[];
     Shared* shared = reinterpret_cast<Shared*>(shared_raw);
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(shared_raw) + sizeof(Shared) + 1023) & ~uintptr_t(1023));
-    constexpr uint32_t kWeightBytes = BM * BK * 2, kInputBytes = kPairHalf * BK * 2, kStageBytes = kWeightBytes + kInputBytes;
-    constexpr uint32_t kColumns = 2 * kPairTokens;   // two accumulators of 256 columns: all of tensor memory
+    constexpr uint32_t kInputBytes = kPairHalf * BK * 2, kWeightBytes = BM * BK * 2, kStageBytes = kInputBytes + kWeightBytes;
+    constexpr uint32_t kColumns = 2 * kPairFeatures;   // two accumulators of 256 columns: all of tensor memory
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int feature_tiles = (N + 2 * BM - 1) / (2 * BM), token_tiles = (M + kPairTokens - 1) / kPairTokens;
+    const int feature_tiles = (N + kPairFeatures - 1) / kPairFeatures, token_tiles = (M + kPairTokens - 1) / kPairTokens;
     const int n_tiles = feature_tiles * token_tiles;
     const int k_blocks = (K + BK - 1) / BK;
     volatile int* abort_flag = &shared->abort_flag;
@@ -568,21 +600,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid
     grid_dependents_launch();   // after this pair holds its tensor memory (see gemm_tc_kernel)
 
     if (warp == 0) {
-        // ---- producer (both blocks): this block's weight rows and its half of the tokens ----------------------
+        // ---- producer (both blocks): this block's 128 tokens and its 128 weight rows -----------------------------
         if (lane == 0) {
             grid_dependency_wait();
             uint32_t stage = 0, phase = 0;
             bool alive = true;
             for (int tile = pair; tile < n_tiles && alive; tile += n_pairs) {
-                const int feature0 = (tile / token_tiles) * (2 * BM) + static_cast<int>(rank) * BM;
                 const int token0 = (tile % token_tiles) * kPairTokens + static_cast<int>(rank) * kPairHalf;
+                const int feature0 = (tile / token_tiles) * kPairFeatures + static_cast<int>(rank) * BM;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!barrier_wait(&shared->empty[stage], phase ^ 1u, abort_flag)) { alive = false; break; }
-                    uint8_t* weight_tile = tiles + stage * kStageBytes;
+                    uint8_t* input_tile = tiles + stage * kStageBytes;
                     const uint32_t first_full = cluster_address(&shared->full[stage], 0);
                     if (rank == 0) barrier_expect_bytes(&shared->full[stage], 2 * kStageBytes);   // the bytes of both blocks
-                    tma_load_2d_pair(weight_tile, &weight_map, kb * BK, feature0, first_full);
-                    tma_load_2d_pair(weight_tile + kWeightBytes, &input_map, kb * BK, token0, first_full);
+                    tma_load_2d_pair(input_tile, &input_map, kb * BK, token0, first_full);
+                    tma_load_2d_pair(input_tile + kInputBytes, &weight_map, kb * BK, feature0, first_full);
                     if (++stage == static_cast<uint32_t>(stages)) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -590,24 +622,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid
     } else if (warp == 1) {
         // ---- MMA issuer: one thread of the first block, for both --------------------------------------------------
         if (lane == 0 && rank == 0) {
-            // M = 256 over the pair, N = 256.
-            const uint32_t descriptor = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairTokens >> 3) << 17) |
-                                        (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+            // M = 256 tokens over the pair, N = 256 features.
+            const uint32_t descriptor = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairFeatures >> 3) << 17) |
+                                        (static_cast<uint32_t>(kPairTokens >> 4) << 24);
             uint32_t stage = 0, phase = 0, local = 0;
             bool alive = true;
             for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
                 const uint32_t slot = local & 1u, use = local >> 1;
                 if (use > 0 && !barrier_wait(&shared->accumulator_empty[slot], (use - 1) & 1u, abort_flag)) { alive = false; break; }
                 tensor_fence_after_sync();
-                const uint32_t accumulator = tensor_base + slot * kPairTokens;
+                const uint32_t accumulator = tensor_base + slot * kPairFeatures;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!barrier_wait(&shared->full[stage], phase, abort_flag)) { alive = false; break; }
                     tensor_fence_after_sync();
-                    const uint32_t weight_address = smem_address(tiles + stage * kStageBytes);
-                    const uint32_t input_address = weight_address + kWeightBytes;
+                    const uint32_t input_address = smem_address(tiles + stage * kStageBytes);
+                    const uint32_t weight_address = input_address + kInputBytes;
 #pragma unroll
                     for (int k = 0; k < BK / kMmaK; ++k) {
-                        mma_issue_pair(accumulator, tile_descriptor(weight_address + k * kMmaK * 2), tile_descriptor(input_address + k * kMmaK * 2),
+                        mma_issue_pair(accumulator, tile_descriptor(input_address + k * kMmaK * 2), tile_descriptor(weight_address + k * kMmaK * 2),
                                        descriptor, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     mma_commit_pair(&shared->empty[stage]);   // frees the stage in both blocks
@@ -617,39 +649,81 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid
             }
         }
     } else {
-        // ---- epilogue (both blocks): this block's 128 features of the tile's 256 tokens ----------------------------
+        // ---- epilogue (both blocks): this block's 128 tokens of the tile's 256 features; a thread owns a token -------
         const int quarter = warp & 3;
         uint32_t local = 0;
         bool alive = true;
         grid_dependency_wait();
         for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
             const uint32_t slot = local & 1u, use = local >> 1;
-            const int feature = (tile / token_tiles) * (2 * BM) + static_cast<int>(rank) * BM + quarter * 32 + lane;
-            const int token0 = (tile % token_tiles) * kPairTokens;
+            const int tile_feature0 = (tile / token_tiles) * kPairFeatures;
+            const int warp_token0 = (tile % token_tiles) * kPairTokens + static_cast<int>(rank) * kPairHalf + quarter * 32;
+            const int token = warp_token0 + lane;
             if (!barrier_wait(&shared->accumulator_full[slot], use & 1u, abort_flag)) { alive = false; break; }
             tensor_fence_after_sync();
-            const float offset = (bias != nullptr && feature < N) ? bias[feature] : 0.0f;
-            const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * kPairTokens;
+            const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * kPairFeatures;
+            const bool row_live = token < M;
+            if (warp_token0 < M) {   // the same for the whole warp
 #pragma unroll 1
-            for (int chunk = 0; chunk < kPairTokens; chunk += 16) {
-                if (token0 + chunk >= M) break;   // the same for every lane
-                uint32_t v[16];
-                tensor_load_16(lane_base + chunk, v);
-                if (Gated) {
-                    const int out_feature = (feature >> 4) * 8 + (feature & 7);
+                for (int chunk = 0; chunk < kPairFeatures; chunk += 32) {
+                    const int feature = tile_feature0 + chunk;
+                    if (feature >= N) break;
+                    uint32_t v[32];
+                    tensor_load_32(lane_base + chunk, v);
+                    tensor_load_wait();
+                    float value[32];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float mine = round_through<bf16>(__uint_as_float(v[j]) + offset);
-                        const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-                        const int token = token0 + chunk + j;
-                        if ((lane & 8) == 0 && feature < N && token < M)
-                            out[static_cast<size_t>(token) * out_stride + out_feature] = from_float<TOut>(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+                    for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(v[j]);
+                    if (bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (feature + j < N) value[j] += __ldg(bias + feature + j);
                     }
-                } else if (feature < N) {
+                    if (!row_live) continue;
+                    if (Gated) {
+                        // Features come in groups of 8 gate values followed by their 8 up values; both are rounded to the
+                        // storage type first, as the unfused product would have stored them.
+                        TOut* target = out + static_cast<size_t>(token) * out_stride + (feature >> 1);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int token = token0 + chunk + j;
-                        if (token < M) out[static_cast<size_t>(token) * out_stride + feature] = from_float<TOut>(__uint_as_float(v[j]) + offset);
+                        for (int group = 0; group < 2; ++group) {
+                            float result[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float gate = round_through<bf16>(value[16 * group + j]), up = round_through<bf16>(value[16 * group + 8 + j]);
+                                result[j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16: the fast forms lose nothing
+                            }
+                            if (feature + 16 * group >= N) break;
+                            if (vector_stores) {
+                                *reinterpret_cast<uint4*>(target + 8 * group) =
+                                    make_uint4(pack_pair(result[0], result[1]), pack_pair(result[2], result[3]), pack_pair(result[4], result[5]),
+                                               pack_pair(result[6], result[7]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) target[8 * group + j] = from_float<TOut>(result[j]);
+                            }
+                        }
+                    } else {
+                        TOut* target = out + static_cast<size_t>(token) * out_stride + feature;
+                        if (vector_stores) {
+                            if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                                for (int group = 0; group < 4; ++group)
+                                    if (feature + 8 * group < N)
+                                        *reinterpret_cast<uint4*>(target + 8 * group) =
+                                            make_uint4(pack_pair(value[8 * group], value[8 * group + 1]), pack_pair(value[8 * group + 2], value[8 * group + 3]),
+                                                       pack_pair(value[8 * group + 4], value[8 * group + 5]), pack_pair(value[8 * group + 6], value[8 * group + 7]));
+                            } else {
+#pragma unroll
+                                for (int group = 0; group < 8; ++group)
+                                    if (feature + 4 * group < N)
+                                        *reinterpret_cast<float4*>(target + 4 * group) =
+                                            make_float4(value[4 * group], value[4 * group + 1], value[4 * group + 2], value[4 * group + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (feature + j < N) target[j] = from_float<TOut>(value[j]);
+                        }
                     }
                 }
             }
@@ -825,7 +899,7 @@ int launch(const CUtensorMap& weight_map, const CUtensorMap& input_map, const fl
 template <typename TOut, bool Gated>
 int launch_pair(const CUtensorMap& weight_map, const CUtensorMap& input_map, const float* bias, void* out, int M, int N, int K,
                 long long out_stride, cudaStream_t stream) {
-    constexpr int stage_bytes = (BM + kPairHalf) * BK * 2;
+    constexpr int stage_bytes = (kPairHalf + BM) * BK * 2;
     int stages = (200 * 1024) / stage_bytes;
     if (stages > 8) stages = 8;
     const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
@@ -835,10 +909,13 @@ int launch_pair(const CUtensorMap& weight_map, const CUtensorMap& input_map, con
         if (status != cudaSuccess) return static_cast<int>(status);
         configured = true;
     }
-    const int tiles = ((N + 2 * BM - 1) / (2 * BM)) * ((M + kPairTokens - 1) / kPairTokens);
+    const int tiles = ((N + kPairFeatures - 1) / kPairFeatures) * ((M + kPairTokens - 1) / kPairTokens);
     const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    // 16-byte stores need rows of the output that start on 16 bytes and whole groups of features inside N.
+    const int group = Gated ? 16 : (sizeof(TOut) == 2 ? 8 : 4);
+    const int vector_stores = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (out_stride * sizeof(TOut)) % 16 == 0 && N % group == 0;
     tau_launch_clusters(2, gemm_tc_pair_kernel<TOut, Gated>, dim3(2 * pairs), dim3(kThreads), shared_bytes, stream, weight_map, input_map, bias,
-                        static_cast<TOut*>(out), M, N, K, out_stride, stages);
+                        static_cast<TOut*>(out), M, N, K, out_stride, stages, vector_stores);
     return tau_launch_status();
 }
 
