@@ -201,6 +201,15 @@ def gemm_simt(values, weight, bias, out) -> None:
 SKINNY_MAX_ROWS = 32      # what the skinny kernel accepts
 SKINNY_BEST_ROWS = 8      # up to here it beats the tcgen05 product cut along K (Qwen3-8B layer shapes: 72 us against 81 us per
                           # layer at 8 rows, 97 against 82 at 12, 152 against 91 at 32)
+SKINNY_SMALL_ROWS = 16    # ... and up to here where the weight is small: the tcgen05 kernel's set-up (tensor memory, barriers,
+SKINNY_SMALL_WEIGHT = 8 << 20   # tensor maps, the meeting of its K ranges) costs about 6 us whatever the size, the skinny kernel's
+                          # about 2.5 us.  Qwen3-0.6B layer shapes (2 to 6 M elements per weight): 18.7 us against 24.4 us per layer
+                          # at 16 rows, 26.0 against 25.9 at 24.  Qwen3-8B shapes (17 to 100 M): 101 against 80 us at 16 rows.
+
+
+def _skinny_wins(values, weight) -> bool:
+    rows = values.shape[0]
+    return rows <= SKINNY_BEST_ROWS or (rows <= SKINNY_SMALL_ROWS and weight.numel() <= SKINNY_SMALL_WEIGHT)
 
 
 def _skinny_fits(values, weight, out) -> bool:
@@ -319,7 +328,7 @@ def gated_fits(in_features: int, out_features: int, dtype) -> bool:
 def linear_gated(values, weight, out) -> None:
     """`out = silu(values @ gate.T) * (values @ up.T)` in one product; `weight` holds groups of 8 gate rows followed by
     their 8 up rows (see `parts.linear.StackedLinear(interleave=...)`)."""
-    if _skinny_fits(values, weight, out) and values.shape[0] <= SKINNY_BEST_ROWS:
+    if _skinny_fits(values, weight, out) and _skinny_wins(values, weight):
         return gemm_skinny(values, weight, None, out, gated=True)
     _require(_tc_fits(values, weight, out), "the gated product needs bfloat16, K % 8 == 0 and 16-byte aligned rows")
     gemm_tc(values, weight, None, out, gated=True)
@@ -328,7 +337,7 @@ def linear_gated(values, weight, out) -> None:
 def linear(values, weight, bias, out) -> None:
     """`out = values @ weight.T + bias` with the kernel that fits the dtype and the sizes."""
     if values.dtype == torch.bfloat16 and _prefer_optimized:
-        if _skinny_fits(values, weight, out) and values.shape[0] <= SKINNY_BEST_ROWS:
+        if _skinny_fits(values, weight, out) and _skinny_wins(values, weight):
             return gemm_skinny(values, weight, bias, out)
         if _tc_fits(values, weight, out):
             return gemm_tc(values, weight, bias, out)
