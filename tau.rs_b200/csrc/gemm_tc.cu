@@ -663,67 +663,112 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid
             tensor_fence_after_sync();
             const uint32_t lane_base = tensor_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * kPairFeatures;
             const bool row_live = token < M;
-            if (warp_token0 < M) {   // the same for the whole warp
-#pragma unroll 1
-                for (int chunk = 0; chunk < kPairFeatures; chunk += 32) {
-                    const int feature = tile_feature0 + chunk;
-                    if (feature >= N) break;
-                    uint32_t v[32];
-                    tensor_load_32(lane_base + chunk, v);
-                    tensor_load_wait();
-                    float value[32];
+            // The values of `count` (a multiple of 32) features from `column` on, bias added: every lane of the warp calls it together.
+            auto load_features = [&](int column, float (&value)[32]) {
+                uint32_t v[32];
+                tensor_load_32(lane_base + column, v);
+                tensor_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(v[j]);
-                    if (bias != nullptr) {
+                for (int j = 0; j < 32; ++j) value[j] = __uint_as_float(v[j]);
+                if (bias != nullptr) {
+                    const int feature = tile_feature0 + column;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (feature + j < N) value[j] += __ldg(bias + feature + j);
+                    for (int j = 0; j < 32; ++j)
+                        if (feature + j < N) value[j] += __ldg(bias + feature + j);
+                }
+            };
+            // silu(gate) * up of the 16 + 16 features in `value` (groups of 8 gate values followed by their 8 up values); both
+            // are rounded to the storage type first, as the unfused product would have stored them.
+            auto gated_pairs = [&](const float (&value)[32], uint32_t* packed) {
+#pragma unroll
+                for (int group = 0; group < 2; ++group) {
+                    float result[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float gate = round_through<bf16>(value[16 * group + j]), up = round_through<bf16>(value[16 * group + 8 + j]);
+                        result[j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16: the fast forms lose nothing
                     }
-                    if (!row_live) continue;
-                    if (Gated) {
-                        // Features come in groups of 8 gate values followed by their 8 up values; both are rounded to the
-                        // storage type first, as the unfused product would have stored them.
-                        TOut* target = out + static_cast<size_t>(token) * out_stride + (feature >> 1);
 #pragma unroll
-                        for (int group = 0; group < 2; ++group) {
-                            float result[8];
+                    for (int j = 0; j < 4; ++j) packed[4 * group + j] = pack_pair(result[2 * j], result[2 * j + 1]);
+                }
+            };
+            if (warp_token0 < M && vector_stores) {   // the same for the whole warp
+                // A lane gathers 128 bytes of its token's output row at a time (64 bfloat16 features, 32 float ones, or the
+                // 64 results of 128 gated ones), the warp turns its 32 x 128 bytes over in shared memory, and then eight lanes
+                // store one row's 128 bytes side by side: a store touches 4 lines of memory and fills them, where the lanes'
+                // own rows would be 32 lines, 16 bytes of each.
+                constexpr int kFeaturesPerPass = Gated ? 128 : (sizeof(TOut) == 2 ? 64 : 32);
+                constexpr int kOutputsPerPass = Gated ? 64 : kFeaturesPerPass;
+                constexpr int kOutputsPerPiece = 16 / static_cast<int>(sizeof(TOut));
+                const uint32_t staging = smem_address(tiles + stages * kStageBytes) + static_cast<uint32_t>(quarter) * 4096u;
+                const int outputs = Gated ? N / 2 : N;
+#pragma unroll 1
+                for (int column = 0; column < kPairFeatures; column += kFeaturesPerPass) {
+                    if (tile_feature0 + column >= N) break;
+                    uint32_t packed[32];
+                    if constexpr (Gated) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float gate = round_through<bf16>(value[16 * group + j]), up = round_through<bf16>(value[16 * group + 8 + j]);
-                                result[j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;   // the result is rounded to bfloat16: the fast forms lose nothing
-                            }
-                            if (feature + 16 * group >= N) break;
-                            if (vector_stores) {
-                                *reinterpret_cast<uint4*>(target + 8 * group) =
-                                    make_uint4(pack_pair(result[0], result[1]), pack_pair(result[2], result[3]), pack_pair(result[4], result[5]),
-                                               pack_pair(result[6], result[7]));
-                            } else {
+                        for (int part = 0; part < 4; ++part) {
+                            float value[32];
+                            load_features(column + 32 * part, value);
+                            gated_pairs(value, packed + 8 * part);
+                        }
+                    } else if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
-                                for (int j = 0; j < 8; ++j) target[8 * group + j] = from_float<TOut>(result[j]);
-                            }
+                        for (int part = 0; part < 2; ++part) {
+                            float value[32];
+                            load_features(column + 32 * part, value);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) packed[16 * part + j] = pack_pair(value[2 * j], value[2 * j + 1]);
                         }
                     } else {
+                        float value[32];
+                        load_features(column, value);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) packed[j] = __float_as_uint(value[j]);
+                    }
+                    __syncwarp();   // the pass before has been read out of the staging rows
+#pragma unroll
+                    for (int piece = 0; piece < 8; ++piece)   // row `lane`; the pieces of a row change places so that eight lanes meet eight banks
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(staging + lane * 128u + ((piece ^ (lane & 7)) << 4)),
+                                     "r"(packed[4 * piece]), "r"(packed[4 * piece + 1]), "r"(packed[4 * piece + 2]), "r"(packed[4 * piece + 3])
+                                     : "memory");
+                    __syncwarp();
+                    const int output0 = (Gated ? (tile_feature0 + column) / 2 : tile_feature0 + column) + (lane & 7) * kOutputsPerPiece;
+#pragma unroll
+                    for (int step = 0; step < 8; ++step) {
+                        const int row = 4 * step + (lane >> 3);
+                        uint4 data;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(data.x), "=r"(data.y), "=r"(data.z), "=r"(data.w)
+                                     : "r"(staging + row * 128u + (((lane & 7) ^ (row & 7)) << 4)));
+                        if (warp_token0 + row < M && output0 < outputs)
+                            *reinterpret_cast<uint4*>(out + static_cast<size_t>(warp_token0 + row) * out_stride + output0) = data;
+                    }
+                }
+                (void)kOutputsPerPass;
+            } else if (warp_token0 < M) {
+                // Rows of the output that do not start on 16 bytes, or a number of features that cuts a group: value by value.
+#pragma unroll 1
+                for (int column = 0; column < kPairFeatures; column += 32) {
+                    const int feature = tile_feature0 + column;
+                    if (feature >= N) break;
+                    float value[32];
+                    load_features(column, value);
+                    if (!row_live) continue;
+                    if (Gated) {
+                        uint32_t packed[8];
+                        gated_pairs(value, packed);
+                        TOut* target = out + static_cast<size_t>(token) * out_stride + (feature >> 1);
+                        const bf16* results = reinterpret_cast<const bf16*>(packed);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (feature + 16 * (j / 8) < N) target[j] = from_float<TOut>(__bfloat162float(results[j]));
+                    } else {
                         TOut* target = out + static_cast<size_t>(token) * out_stride + feature;
-                        if (vector_stores) {
-                            if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
-                                for (int group = 0; group < 4; ++group)
-                                    if (feature + 8 * group < N)
-                                        *reinterpret_cast<uint4*>(target + 8 * group) =
-                                            make_uint4(pack_pair(value[8 * group], value[8 * group + 1]), pack_pair(value[8 * group + 2], value[8 * group + 3]),
-                                                       pack_pair(value[8 * group + 4], value[8 * group + 5]), pack_pair(value[8 * group + 6], value[8 * group + 7]));
-                            } else {
-#pragma unroll
-                                for (int group = 0; group < 8; ++group)
-                                    if (feature + 4 * group < N)
-                                        *reinterpret_cast<float4*>(target + 4 * group) =
-                                            make_float4(value[4 * group], value[4 * group + 1], value[4 * group + 2], value[4 * group + 3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (feature + j < N) target[j] = from_float<TOut>(value[j]);
-                        }
+                        for (int j = 0; j < 32; ++j)
+                            if (feature + j < N) target[j] = from_float<TOut>(value[j]);
                     }
                 }
             }
@@ -902,7 +947,7 @@ int launch_pair(const CUtensorMap& weight_map, const CUtensorMap& input_map, con
     constexpr int stage_bytes = (kPairHalf + BM) * BK * 2;
     int stages = (200 * 1024) / stage_bytes;
     if (stages > 8) stages = 8;
-    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes;
+    const int shared_bytes = sizeof(Shared) + 1024 + stages * stage_bytes + 4 * 4096;   // and the epilogue warps' staging rows
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut, Gated>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);

@@ -312,7 +312,8 @@ def test_the_plain_implementation_at_the_width_of_a_real_model(tmp_path, dtype):
 @pytest.mark.parametrize("length,config", [(5000, MEDIUM), (9000, OTHER_MEDIUM)], ids=["5000_d128", "9000_d64"])
 def test_a_long_context_at_the_width_of_a_real_model(tmp_path, length, config):
     """One layer in bfloat16 over thousands of positions against the plain implementation: the prompt whole (dozens of
-    query tiles and up to 141 key tiles of the tensor-memory attention), then six tokens one by one over a context that
+    query tiles and up to 141 key tiles of the tensor-memory attention; the first and the last row of every 64 are
+    compared, each on its own), then six tokens one by one over a context that
     decode attention cuts into 16 blocks of one cluster (5,000 positions) or 32 that meet in global memory (9,000)."""
     from tau_rs_b200.csrc import kernels
     from tau_rs_b200.weights import write_random_model
@@ -325,9 +326,11 @@ def test_a_long_context_at_the_width_of_a_real_model(tmp_path, length, config):
     engine = engine_for(folder, "bfloat16", "gpu", 64 * 160)
     assert engine.decode_splits(1, length + 1) == (16 if length <= 8192 else 32)
     slot = engine.open_sequence()
-    places = [0, 63, 64, length // 2, length - 2, length - 1]
+    places = sorted(set(list(range(0, length, 64)) + list(range(63, length, 64)) + [length // 2, length - 2, length - 1]))
     logits = engine.step([StepEntry(slot, tokens[:length], places)]).float().cpu()
     assert relative_error(logits, wanted[places]) < TOLERANCE["bfloat16"]
+    for row, place in enumerate(places):     # row by row: one query tile's lost keys must not hide behind another row's largest logit
+        assert relative_error(logits[row], wanted[place]) < TOLERANCE["bfloat16"], place
     for index in range(length, length + 6):
         logits = engine.step([StepEntry(slot, [tokens[index]], [0])]).float().cpu()
         assert relative_error(logits, wanted[index : index + 1]) < TOLERANCE["bfloat16"]
