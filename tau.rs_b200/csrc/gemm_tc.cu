@@ -1010,10 +1010,11 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
         const int feature_tiles = (N + BM - 1) / BM, tiles = feature_tiles * ((M + 255) / 256);
         if (choose_splits(M, tiles, (K + BK - 1) / BK, sm_count(), workspace_floats, 256 * BM) > 1) {
             paired = false;
-        } else if (token_box == 0) {
+        } else if (token_box == 0 && M <= 1024) {
             // Between the batches that are cut along K and the prompts that fill every SM several times, the token tile
             // decides how many SMs have work: 512 tokens of a 6144-feature product are 96 tiles of 256 tokens, but 144
-            // of 192.  An estimate of waves x (tokens of a tile + a fixed part) picks among 256, 192 and 128.
+            // of 192.  An estimate of waves x (tokens of a tile + a fixed part) picks among 256, 192 and 128.  Beyond 1,024
+            // tokens the pairs always win (6,328 tokens of a gated 6144 x 1024 product: 195 us in tiles of 192 on single SMs).
             int best = 256;
             long long best_cost = 0;
             for (int candidate : {256, 192, 128}) {
