@@ -550,3 +550,40 @@ def test_argmax_calls_in_a_row_share_their_scratch():
         assert torch.equal(valid.cpu().bool(), is_valid)
         assert torch.equal(tokens.cpu()[is_valid].long(), last_best[is_valid])
         assert int(tokens[rows // 2]) == 0 and int(valid[rows // 2]) == 0
+
+
+@pytest.mark.parametrize("head_dim,length", [(128, 6000), (64, 4000)])
+def test_prefill_attention_counts_every_key_tile_of_a_long_context(head_dim, length):
+    """Thousands of positions with inputs made so that a lost key tile shows in every row: all queries are zero, so a row
+    attends evenly to every key it may see, and the value of key k is 1 in column k // 64 and 0 elsewhere; row p must then
+    hold `visible keys of tile c / (p + 1)` in column c, exactly up to the output's rounding.  Whole, and as a second run
+    behind 3,000 cached positions (one wrong row among thousands was how a race in the hand-over of value tiles once showed)."""
+    n_heads, n_kv_heads = 2, 1
+    assert length // 64 < head_dim
+    n_pages = (length + 63) // 64
+    generator = torch.Generator().manual_seed(7)
+    order = torch.randperm(n_pages + 5, generator=generator)[:n_pages].to(torch.int32)
+    keys = torch.randn(n_pages + 5, n_kv_heads, 64, head_dim, generator=generator).to(torch.bfloat16).to(DEVICE)
+    values = torch.zeros(n_pages + 5, n_kv_heads, 64, head_dim, dtype=torch.bfloat16, device=DEVICE)
+    for tile in range(n_pages):
+        values[int(order[tile]), 0, :, tile] = 1.0
+        if tile == n_pages - 1 and length % 64:
+            values[int(order[tile]), 0, length % 64:] = float("nan")      # beyond the sequence: never read into a result
+    rows = order.view(1, n_pages).to(DEVICE).contiguous()
+    position = torch.arange(length, dtype=torch.float32)
+    wanted = torch.zeros(length, head_dim)
+    for tile in range(n_pages):
+        wanted[:, tile] = (position + 1 - 64 * tile).clamp(0, 64) / (position + 1)
+    for start in (0, 3000):
+        new = length - start
+        queries = torch.zeros(new, n_heads * head_dim, dtype=torch.bfloat16, device=DEVICE)
+        found = torch.full_like(queries, float("nan"))
+        cu = torch.tensor([0, new], dtype=torch.int32, device=DEVICE)
+        starts = torch.tensor([start], dtype=torch.int32, device=DEVICE)
+        kernels.attention_prefill_tc(queries, keys, values, found, cu, starts, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, 0)
+        assert kernels.attention_prefill_tc_status(head_dim) == 0
+        for head in range(n_heads):
+            got = found.view(new, n_heads, head_dim)[:, head].float().cpu()
+            error = (got - wanted[start:]).abs()
+            worst = int(error.max(dim=1).values.argmax())
+            assert float(error.max()) <= 2 ** -8 * float(wanted[start:].max()), (start, head, start + worst, float(error.max()))
