@@ -195,6 +195,31 @@ __device__ __forceinline__ float fast_exp2(float value) {
     return result;
 }
 
+// Two 32-bit floats in one 64-bit register for the packed arithmetic of sm_100 (one instruction, two results): the softmax
+// warps are bound by the instructions they issue, and half of a row's scalings and sums are instructions saved.
+typedef unsigned long long Float2;
+__device__ __forceinline__ Float2 pair_of(float low, float high) {
+    Float2 pair;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(pair) : "f"(low), "f"(high));
+    return pair;
+}
+__device__ __forceinline__ void unpair(Float2 pair, float& low, float& high) { asm("mov.b64 {%0, %1}, %2;" : "=f"(low), "=f"(high) : "l"(pair)); }
+__device__ __forceinline__ Float2 fma_pair(Float2 a, Float2 b, Float2 c) {
+    Float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ Float2 add_pair(Float2 a, Float2 b) {
+    Float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max_of_three(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
     const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
     return *reinterpret_cast<const unsigned*>(&pair);
@@ -420,7 +445,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             }
             float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < BN; ++j) partial_max[j & 3] = fmaxf(partial_max[j & 3], score[j]);
+            for (int j = 0; j < BN; j += 2) partial_max[(j >> 1) & 3] = max_of_three(partial_max[(j >> 1) & 3], score[j], score[j + 1]);
             // Of the raw scores; the scale is positive and is applied afterwards.
             float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3]));
             tile_max *= scale_log2;
@@ -465,16 +490,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // Probabilities: this row's 64 values as 32 pairs of bfloat16, written over the row's scores in tensor memory,
             // where the second product takes them as its A operand.
             uint32_t packed[BN / 2];
-            float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            Float2 partial_sum[4] = {pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f)};
+            const Float2 scale_pair = pair_of(scale_log2, scale_log2), shift_pair = pair_of(-subtract, -subtract);
 #pragma unroll
             for (int j = 0; j < BN; j += 2) {
-                const float p0 = fast_exp2(fmaf(score[j], scale_log2, -subtract));
-                const float p1 = fast_exp2(fmaf(score[j + 1], scale_log2, -subtract));
-                partial_sum[j & 3] += p0;
-                partial_sum[(j + 1) & 3] += p1;
+                float x0, x1;
+                unpair(fma_pair(pair_of(score[j], score[j + 1]), scale_pair, shift_pair), x0, x1);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                partial_sum[(j >> 1) & 3] = add_pair(partial_sum[(j >> 1) & 3], pair_of(p0, p1));
                 packed[j / 2] = pack_bf16(p0, p1);
             }
-            sum += (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
+            {
+                float low, high;
+                unpair(add_pair(add_pair(partial_sum[0], partial_sum[1]), add_pair(partial_sum[2], partial_sum[3])), low, high);
+                sum += low + high;
+            }
             tensor_store_words_32(lane_base + (i & 1) * BN, packed);
             if (key0 + BN - 1 > last_position) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared value rows, for the tensor core's reads
             tensor_fence_before_sync();
