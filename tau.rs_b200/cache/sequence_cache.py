@@ -94,9 +94,11 @@ class SequenceCache:
             raise ValueError("the cache must hold at least one token")
         self.device, self.dtype = device, dtype
         self.n_pages = pages_for(max_tokens)
-        # A sequence cannot hold more pages than there are, unless every kv group lets old pages go (a window).
+        # A sequence cannot hold more pages than there are, unless every kv group lets old pages go (a window) or the model
+        # keeps no keys and values at all (state of fixed size only).
         kv_needs = [need for need, _ in groups.values() if need.kind == "kv"]
-        bounded = bool(kv_needs) and all(need.window for need in kv_needs)
+        bounded = all(need.window for need in kv_needs)
+        self.widest_window = max((need.window for need in kv_needs), default=0) if bounded else None
         self.pages_per_sequence = pages_for(max_sequence_tokens) if bounded else min(self.n_pages, pages_for(max_sequence_tokens))
         self.max_sequence_tokens = min(max_sequence_tokens, self.pages_per_sequence * PAGE_TOKENS)
         self.n_slots = min(self.n_pages, max_slots) if max_slots else self.n_pages

@@ -95,3 +95,6 @@ class ModelSpec:
     tie_head: bool
     declared_dtype: Optional[str] = None
     extra: dict = field(default_factory=dict, compare=False)
+    # A position encoding that acts on the embedded tokens before the first block (learned or absolute positions): a spec of
+    # the "position" family whose part offers `add_to(hidden, step)`.  None for encodings that act inside the mixers.
+    input_position: Optional[object] = None

@@ -118,7 +118,7 @@ class GenerationMetrics:
 def plan_batches(needs: Sequence[int], max_batch: int, capacity_tokens: int) -> List[List[int]]:
     """Splits request numbers `0..n` into consecutive batches.
 
-    `needs[i]` is the most tokens request `i` can come to hold.  A batch has at most
+    `needs[i]` is the most tokens request `i` can come to hold at one time.  A batch has at most
     `max_batch` requests and its needs, each rounded up to whole pages, fit the cache.
     """
     batches: List[List[int]] = []
@@ -184,7 +184,10 @@ def generate_tokens(backend, prompts: Sequence[Sequence[int]], max_new_tokens, s
             results[index] = GenerationResult([], "length", len(prompt))
         else:
             active.append(index)
-    needs = [len(prompts[index]) + limits[index] for index in active]
+    # What a request holds in the cache at most: its whole length, unless the backend knows better (windows let pages go).
+    peak = getattr(backend, "peak_cache_tokens", None)
+    needs = [len(prompts[index]) + limits[index] if peak is None
+             else peak(len(prompts[index]), len(prompts[index]) + limits[index], prefill_chunk_tokens) for index in active]
     for batch in plan_batches(needs, max_batch, backend.capacity_tokens):
         metrics.batches += 1
         _run_batch(backend, [active[position] for position in batch], prompts, limits, select, stop,

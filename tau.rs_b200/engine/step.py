@@ -97,6 +97,17 @@ class Engine:
     def max_sequence_tokens(self) -> int:
         return self.cache.max_sequence_tokens
 
+    def peak_cache_tokens(self, prompt_tokens: int, total_tokens: int, chunk: Optional[int] = None) -> int:
+        """The most cache positions that a request holds at any one time if its prompt enters in runs of at most `chunk`
+        tokens and it grows to `total_tokens`: all of them, unless every group of keys and values has a window (then the
+        widest window, one run and the slack of whole pages) or the model keeps none at all."""
+        if not self.cache.kv:
+            return 0
+        if self.cache.widest_window is None:
+            return total_tokens
+        run = min(prompt_tokens, chunk) if chunk else prompt_tokens
+        return min(total_tokens, self.cache.widest_window + run + 3 * PAGE_TOKENS)
+
     def bytes_read_by_a_decode_step(self) -> int:
         """Every weight once, and the cached keys and values of the live sequences: what a decode step of all of them reads."""
         if self._weight_bytes is None:

@@ -43,6 +43,19 @@ class Part:
     def finalize_weights(self) -> None:
         pass
 
+    def bytes_read_per_step(self, dtype) -> int:
+        """Bytes of this part's weights that one step reads: every tensor once, unless the part knows better (a feed-forward
+        that routes each token to a few of its experts reads only those).  The roofline of a decode step is built on it."""
+        from ..weights.loader import device_dtype
+
+        total = 0
+        for spec in self.tensor_specs().values():
+            count = 1
+            for extent in spec.shape:
+                count *= extent
+            total += count * torch.empty((), dtype=device_dtype(spec, dtype)).element_size()
+        return total
+
 
 class Mixer(Part):
     """Mixes information between the tokens of a sequence.

@@ -55,6 +55,9 @@ class PreNormBlock(Block):
         for part in self._children:
             part.finalize_weights()
 
+    def bytes_read_per_step(self, dtype) -> int:
+        return sum(part.bytes_read_per_step(dtype) for part in self._children)
+
     def forward(self, residual, branch, step, cache, writes_cache: bool):
         if branch is None:
             normalized = self.mixer_norm.forward(residual)

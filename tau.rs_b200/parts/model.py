@@ -23,10 +23,12 @@ class DecoderModel:
         self.spec, self.dtype, self.device = spec, dtype, device
         self.blocks = [build("block", block, dtype=dtype, device=device) for block in spec.blocks]
         self.final_norm = build("norm", spec.final_norm, name=spec.final_norm_name, dtype=dtype, device=device)
+        self.input_position = None if spec.input_position is None else build("position", spec.input_position, device=device)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self._owner: Dict[str, object] = {}
-        for part in (*self.blocks, self.final_norm):
+        self._parts = (*self.blocks, self.final_norm) + (() if self.input_position is None else (self.input_position,))
+        for part in self._parts:
             for name in part.tensor_specs():
                 if name in self._owner:
                     raise ValueError(f"two parts ask for the tensor {name}")
@@ -66,7 +68,7 @@ class DecoderModel:
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         spec = self.spec
         specs = {spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden), role="matrix")}
-        for part in (*self.blocks, self.final_norm):
+        for part in self._parts:
             specs.update(part.tensor_specs())
         if not spec.tie_head:
             specs[spec.head_name] = TensorSpec((spec.vocab_size, spec.hidden), role="matrix", fallback=spec.embedding_name)
@@ -89,26 +91,18 @@ class DecoderModel:
             self._owner[name].assign(name, tensor)
 
     def finalize_weights(self) -> None:
-        for part in (*self.blocks, self.final_norm):
+        for part in self._parts:
             part.finalize_weights()
         if self.spec.tie_head:
             self.head = self.embedding
 
     def weight_bytes(self) -> int:
-        """Bytes of every weight tensor that one step reads once (the embedding table is read by row, so it
-        counts only where it is the head as well; a block that the schedule never names is left out)."""
-        from ..weights.loader import device_dtype
-
+        """Bytes of weights that one step reads: what each part says it reads (every tensor once, unless a part knows
+        better), the head, and nothing of the embedding table, which is read by row (it counts only where it is the head
+        as well); a block that the schedule never names is left out."""
         scheduled = {entry.layer for entry in self.spec.schedule}
-        total = 0
-        for index, part in enumerate((*self.blocks, self.final_norm)):
-            if index < len(self.blocks) and index not in scheduled:
-                continue
-            for spec in part.tensor_specs().values():
-                count = 1
-                for extent in spec.shape:
-                    count *= extent
-                total += count * torch.empty((), dtype=device_dtype(spec, self.dtype)).element_size()
+        total = sum(block.bytes_read_per_step(self.dtype) for index, block in enumerate(self.blocks) if index in scheduled)
+        total += self.final_norm.bytes_read_per_step(self.dtype)
         return total + self.spec.vocab_size * self.spec.hidden * torch.empty((), dtype=self.dtype).element_size()
 
     def decode_splits(self, n_seqs: int, max_len: int) -> int:
@@ -122,6 +116,8 @@ class DecoderModel:
         spec = self.spec
         residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.dtype, device=self.device)
         kernels.embedding(step.token_ids, self.embedding, residual)
+        if self.input_position is not None:
+            self.input_position.add_to(residual, step)
         branch = None
         for entry in spec.schedule:
             view = None if entry.cache_group is None else cache.layer_view(entry.cache_group, entry.cache_layer)

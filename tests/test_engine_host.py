@@ -148,3 +148,32 @@ def test_windowed_layers_give_pages_back_and_lose_nothing(cpu_kernels, tmp_path)
         windowed_cache_matches_whole_prompt(folder, "float32", torch.device("cpu"), 1e-4)
     finally:
         unregister_architecture("ToyWindowForCausalLM")
+
+
+def test_generation_plans_windowed_requests_by_what_they_hold_at_once(cpu_kernels, tmp_path):
+    """Where every group of keys and values has a window, a request holds about a window and one run of pages however long
+    it grows: the generation loop runs requests of up to 500 tokens through a cache of 9 pages (576 positions), two at a time, and
+    gives the tokens that a roomy cache gives.  Without a window the same plan is refused."""
+    from helpers import WINDOW_CONFIG, window_spec
+    from tau_rs_b200 import Engine, generate, load_model, write_random_model
+    from tau_rs_b200.config import register_architecture, unregister_architecture
+
+    register_architecture("ToyWindowForCausalLM", "toy_window", lambda raw: raw, window_spec)
+    try:
+        folder = str(tmp_path / "window")
+        write_random_model(folder, WINDOW_CONFIG, seed=9, norm_jitter=0.1, storage="float32")
+        model = load_model(folder, "float32", torch.device("cpu"))
+        prompts = random_prompts(WINDOW_CONFIG["vocab_size"], [400, 30, 260], seed=14)
+        roomy = generate(Engine(model, 64 * 40), prompts, max_new_tokens=100, stop_tokens=(), prefill_chunk_tokens=32)
+        tight_engine = Engine(model, 64 * 9)
+        assert tight_engine.peak_cache_tokens(400, 500, 32) == 70 + 32 + 3 * 64 and tight_engine.peak_cache_tokens(400, 500) == 500
+        assert tight_engine.peak_cache_tokens(30, 130, 32) == 130
+        tight = generate(tight_engine, prompts, max_new_tokens=100, stop_tokens=(), prefill_chunk_tokens=32, max_batch=2)
+        assert [result.tokens for result in tight] == [result.tokens for result in roomy]
+        assert tight.metrics.batches == 2
+        tight_engine.cache.check()
+        assert tight_engine.cache.slots.in_use == 0 and tight_engine.cache.free_tokens() == 64 * 9
+        with pytest.raises(ValueError, match="cache tokens"):
+            generate(Engine(model, 64 * 6), prompts, max_new_tokens=100, stop_tokens=())      # whole prompts in one run: 500 positions do not fit 384
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")

@@ -320,6 +320,12 @@ class RoutedFeedForward(FeedForward):
     def forward(self, hidden, step):
         return routed_feed_forward(hidden.float(), self.tensors, self.prefix, self.spec).to(hidden.dtype)
 
+    def bytes_read_per_step(self, dtype):
+        """A token reads the router and its `top` experts; the largest experts bound what a step of one token reads."""
+        element = torch.empty((), dtype=dtype).element_size()
+        largest = sorted(self.spec.widths, reverse=True)[: self.spec.top]
+        return len(self.spec.widths) * self.spec.hidden * 4 + sum(3 * width * self.spec.hidden * element for width in largest)
+
 
 def routed_feed_forward(x, weights, prefix, spec):
     scores = torch.softmax(x @ weights[f"{prefix}.router.weight"].float().t(), dim=-1)
@@ -455,9 +461,110 @@ def test_a_toy_routed_feed_forward_and_another_position_encoding(routed_architec
     for slot in slots:
         engine.close_sequence(slot)
     engine.cache.check()
+    # The roofline's bytes follow what the routed part says it reads: two of its three experts, not all of them.
+    every_tensor = sum(tensor.numel() * tensor.element_size() for tensor in model.blocks[0].feed_forward.tensors.values())
+    told = model.blocks[0].feed_forward.bytes_read_per_step(torch.float32)
+    assert told == 3 * 24 * 4 + 3 * (40 + 16) * 24 * 4 < every_tensor
+    assert model.weight_bytes() == (sum(block.bytes_read_per_step(torch.float32) for block in model.blocks)
+                                    + model.final_norm.bytes_read_per_step(torch.float32) + 61 * 24 * 4)
+    assert model.blocks[1].feed_forward.bytes_read_per_step(torch.float32) == 3 * 40 * 24 * 4      # a dense part reads every tensor
     # The slowdown is felt: the same weights with the usual tables give other logits.
     usual = plain_model.rope_tables(16, 500.0, 160)
     assert not torch.allclose(torch.stack(slowed_tables(spec.blocks[0].mixer.position)), torch.stack(usual))
+
+
+# ---- a position encoding that acts at the embedding -------------------------------------------------------------------
+class LearnedPositionsSpec:
+    kind = "toy_learned_positions"
+
+    def __init__(self, hidden, max_positions, name):
+        self.hidden, self.max_positions, self.name = hidden, max_positions, name
+
+    def __eq__(self, other):
+        return isinstance(other, LearnedPositionsSpec) and vars(self) == vars(other)
+
+    def __hash__(self):
+        return hash(tuple(sorted(vars(self).items())))
+
+
+class LearnedPositions(Part):
+    """`h_t = E[token_t] + P[position_t]`: a table of one vector per position, added to the embedded tokens before the first
+    block.  A model names it as `ModelSpec.input_position`; its part offers `add_to(hidden, step)`."""
+
+    def __init__(self, spec, device):
+        self.spec, self.table = spec, None
+
+    def tensor_specs(self):
+        return {self.spec.name: TensorSpec((self.spec.max_positions, self.spec.hidden), role="matrix", std=0.5)}
+
+    def assign(self, name, tensor):
+        self.table = tensor
+
+    def add_to(self, hidden, step):
+        hidden.add_(self.table.index_select(0, step.positions.long()).to(hidden.dtype))
+
+
+def absolute_spec(config) -> ModelSpec:
+    """Dense Qwen3 blocks without any rotation, positions learned and added at the embedding."""
+    hidden = config["hidden_size"]
+    norm = NormSpec(width=hidden, eps=config["eps"])
+    attention = AttentionSpec(hidden=hidden, n_heads=4, n_kv_heads=2, head_dim=16, bias=False, softmax_scale=0.25,
+                              qk_norm=NormSpec(width=16, eps=config["eps"]), position=None)
+    feed = SwiGLUSpec(hidden=hidden, intermediate=config["intermediate_size"])
+    blocks = tuple(BlockSpec(f"model.layers.{index}", attention, feed, norm, norm) for index in range(2))
+    schedule = tuple(ScheduleEntry(layer=index, cache_group="attention", cache_layer=index) for index in range(2))
+    return ModelSpec(architecture="ToyAbsoluteForCausalLM", vocab_size=config["vocab_size"], hidden=hidden, max_positions=config["max_positions"],
+                     embedding_name="model.embed_tokens.weight", blocks=blocks, schedule=schedule, final_norm=norm,
+                     final_norm_name="model.norm.weight", head_name="lm_head.weight", tie_head=True,
+                     input_position=LearnedPositionsSpec(hidden, config["max_positions"], "model.embed_positions.weight"))
+
+
+@pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 2e-2)])
+def test_a_toy_position_encoding_that_acts_at_the_embedding(dtype, tolerance, tmp_path):
+    """Learned absolute positions, registered, built and stepped without a change to the library: whole prompts, an unequal
+    batch and single tokens (through captured graphs on the GPU), against the plain blocks with a rotation of angle zero."""
+    config = {"architectures": ["ToyAbsoluteForCausalLM"], "model_type": "toy_absolute", "hidden_size": 64, "intermediate_size": 96,
+              "vocab_size": 83, "max_positions": 128, "eps": 1e-6}
+    register_position("toy_learned_positions")(LearnedPositions)
+    register_architecture("ToyAbsoluteForCausalLM", "toy_absolute", lambda raw: raw, absolute_spec)
+    try:
+        folder = str(tmp_path / "absolute")
+        write_random_model(folder, config, seed=8, norm_jitter=0.1, storage=dtype)
+        engine = Engine(load_model(folder, dtype, DEVICE), 64 * 6)
+        weights = plain_model.read_plain_weights(folder)
+        rounding = plain_model.bfloat16_rounding if dtype == "bfloat16" else plain_model.no_rounding
+        plain_config = plain_model.PlainConfig(vocab_size=83, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                               num_key_value_heads=2, head_dim=16, attention_bias=False, rms_norm_eps=1e-6, rope_theta=1.0,
+                                               max_position_embeddings=128, tie_word_embeddings=True)
+        no_turn = (torch.ones(128, 8), torch.zeros(128, 8))
+
+        def expected(tokens):
+            hidden = rounding(plain_model.embedding(weights["model.embed_tokens.weight"], tokens) + weights["model.embed_positions.weight"][: len(tokens)])
+            for layer in range(2):
+                hidden = plain_model.decoder_block(hidden, weights, f"model.layers.{layer}", plain_config, *no_turn, rounding)
+            hidden = plain_model.rms_norm(hidden, weights["model.norm.weight"], 1e-6, rounding)
+            return hidden @ weights["model.embed_tokens.weight"].t()
+
+        rng = np.random.default_rng(2)
+        requests = [rng.integers(0, 83, size=length).tolist() for length in (90, 33, 7)]
+        wanted = [expected(tokens) for tokens in requests]
+        slots = [engine.open_sequence() for _ in requests]
+        cuts = [70, 20, 3]
+        logits = engine.step([StepEntry(slot, tokens[:cut], [0, cut - 1]) for slot, tokens, cut in zip(slots, requests, cuts)]).float().cpu()
+        for row, cut in enumerate(cuts):
+            assert error(logits[2 * row], wanted[row][0]) < tolerance and error(logits[2 * row + 1], wanted[row][cut - 1]) < tolerance
+        for offset in range(4):
+            logits = engine.step([StepEntry(slots[i], [requests[i][cuts[i] + offset]], [0]) for i in range(3)]).float().cpu()
+            for i in range(3):
+                assert error(logits[i], wanted[i][cuts[i] + offset]) < tolerance
+        for slot in slots:
+            engine.close_sequence(slot)
+        engine.cache.check()
+        # The positions are felt: a token's logits at position 0 and at position 5 differ although nothing is rotated.
+        assert error(wanted[0][0], expected([requests[0][0]] * 6)[5]) > 1e-2
+    finally:
+        unregister_architecture("ToyAbsoluteForCausalLM")
+        unregister("position", "toy_learned_positions")
 
 
 @pytest.mark.parametrize("dtype,tolerance", [("float32", 1e-4), ("bfloat16", 2e-2)])
