@@ -104,12 +104,13 @@ class GenerateOutput:
 
 def generate(model, prompts: Sequence[Sequence[int]], max_new_tokens=None, temperature: float = 0.0, seed: int = 0,
              stop_tokens: Optional[Sequence[int]] = None, dtype: str = "auto", device="gpu", max_tokens: Optional[int] = None,
-             max_batch: int = 64, prefill_chunk_tokens: Optional[int] = 8192) -> GenerateOutput:
+             max_batch: int = 64, prefill_chunk_tokens: Optional[int] = 8192, metrics: Optional[GenerationMetrics] = None) -> GenerateOutput:
     """Generates token ids for prompts of token ids.
 
     `model` is a model folder, a `DecoderModel` or an `Engine`.  `max_new_tokens` defaults to
     the folder's generation settings (16 if it has none) and `stop_tokens` to its
-    `eos_token_id`.  `temperature == 0` is greedy.  Results keep the prompts' order.
+    `eos_token_id`.  `temperature == 0` is greedy.  Results keep the prompts' order.  `metrics` may bring a
+    `GenerationMetrics` of the caller's (with a `sink` and a `log_interval_s`, say, to watch the decode rate while it runs).
     """
     if isinstance(model, Engine):
         engine = model
@@ -127,7 +128,7 @@ def generate(model, prompts: Sequence[Sequence[int]], max_new_tokens=None, tempe
     if stop_tokens is None:
         stop_tokens = settings.eos_token_ids
     sampler = Sampler(SamplingParams(temperature=temperature, seed=seed))
-    metrics = GenerationMetrics()
+    metrics = metrics if metrics is not None else GenerationMetrics()
     results = generate_tokens(engine, prompts, max_new_tokens, sampler, stop_tokens, max_batch,
                               prefill_chunk_tokens, metrics)
     return GenerateOutput(results, metrics)
