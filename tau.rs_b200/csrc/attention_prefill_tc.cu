@@ -257,6 +257,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &shared->abort_flag;
 
+    if (warp == 4 && lane == 0) {   // the descriptors of the three copies, on their way before the first copy asks for them
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&q_map)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map)) : "memory");
+    }
     if (threadIdx.x == 0) {
         barrier_init(&shared->q_full, 1);
         for (int s = 0; s < kKeyStages; ++s) {
@@ -514,20 +519,38 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         if (alive && n_tiles > 0 && barrier_wait(&shared->pv_done, (n_tiles - 1) & 1u, abort_flag)) {
             tensor_fence_after_sync();
             const float inverse = 1.0f / sum;
-            bf16* target = out + (static_cast<size_t>(row0 + block * BM + row) * n_heads + head) * D;
+            // Every product is done, so the place of the Q tile is free: the rows go there as bfloat16 (16-byte pieces,
+            // exchanged among a row's first eight by the row's number so that neighbouring rows fall into different
+            // banks), and each warp then writes its own 32 rows with whole lines, 32 / (D / 8) rows to an instruction.  A
+            // thread that wrote its row straight from its registers would touch 32 lines with every instruction.
+            uint8_t* staging = q_tile + row * (D * 2);
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 float part[32];
                 tensor_load_32(lane_base + kOColumn + c * 32, part);   // every thread of the warp takes part in the load
                 tensor_load_wait();
-                if (row < rows_here) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        const uint4 packed = make_uint4(pack_bf16(part[j] * inverse, part[j + 1] * inverse), pack_bf16(part[j + 2] * inverse, part[j + 3] * inverse),
-                                                        pack_bf16(part[j + 4] * inverse, part[j + 5] * inverse), pack_bf16(part[j + 6] * inverse, part[j + 7] * inverse));
-                        *reinterpret_cast<uint4*>(target + c * 32 + j) = packed;
-                    }
+                for (int j = 0; j < 32; j += 8) {
+                    const uint4 packed = make_uint4(pack_bf16(part[j] * inverse, part[j + 1] * inverse), pack_bf16(part[j + 2] * inverse, part[j + 3] * inverse),
+                                                    pack_bf16(part[j + 4] * inverse, part[j + 5] * inverse), pack_bf16(part[j + 6] * inverse, part[j + 7] * inverse));
+                    const int piece = c * 4 + j / 8;
+                    *reinterpret_cast<uint4*>(staging + ((piece ^ (row & 7)) << 4)) = packed;
                 }
+            }
+            __syncwarp();
+            constexpr int kPieces = D / 8, kRowsAtOnce = 32 / kPieces;
+            const int piece = lane % kPieces;
+            uint4 line[32 / kRowsAtOnce];
+#pragma unroll
+            for (int step = 0; step < 32 / kRowsAtOnce; ++step) {
+                const int r = warp * 32 + step * kRowsAtOnce + lane / kPieces;
+                line[step] = *reinterpret_cast<const uint4*>(q_tile + r * (D * 2) + ((piece ^ (r & 7)) << 4));
+            }
+#pragma unroll
+            for (int step = 0; step < 32 / kRowsAtOnce; ++step) {
+                const int r = warp * 32 + step * kRowsAtOnce + lane / kPieces;
+                if (r < rows_here)
+                    *reinterpret_cast<uint4*>(out + (static_cast<size_t>(row0 + block * BM + r) * n_heads + head) * D + piece * 8) = line[step];
             }
         }
     }
