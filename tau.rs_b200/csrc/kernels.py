@@ -529,6 +529,9 @@ def attention_prefill(queries, keys, values, out, cu_seqlens, seq_start, page_ro
         ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _stream()), "attention_prefill")
 
 
+_prefill_schedule = {}   # (device, stream) -> the two counters by which the blocks of the tensor-core prefill kernel share out its tiles
+
+
 def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
                          scale: float, window: int) -> None:
     """The same as `attention_prefill` on the tcgen05 tensor cores (accumulators in tensor memory); head sizes 64 and 128."""
@@ -547,10 +550,15 @@ def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page
     _require(cu_seqlens.numel() == n_seqs + 1 and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
              and page_rows.shape[0] == n_seqs, "one run and one row of pages per sequence")
     library = build.load_library("attention_prefill_tc.cu", (f"TAU_HEAD_DIM={head_dim}",))
+    key = (out.device, torch.cuda.current_stream().cuda_stream)
+    schedule = _prefill_schedule.get(key)
+    if schedule is None:   # zero once; the kernel leaves it at zero
+        schedule = _prefill_schedule[key] = torch.zeros(2, dtype=torch.int32, device=out.device)
     _check(library.tau_attention_prefill_tc(
         _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(cu_seqlens), _pointer(seq_start), _pointer(page_rows),
         ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_longlong(keys.shape[0]), ctypes.c_int(n_seqs),
-        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), _stream()),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window),
+        _pointer(schedule), _stream()),
         "attention_prefill_tc")
 
 
