@@ -327,6 +327,35 @@ def test_prefill_attention_tensor_memory_kernel(n_heads, n_kv_heads, head_dim, w
         assert torch.allclose(got, values[int(rows[5, 0]), 0, 5].float(), atol=0.05, rtol=0.05)
 
 
+def test_prefill_attention_shares_more_tiles_than_blocks_out_and_leaves_its_counter_at_zero():
+    """The tcgen05 prefill kernel's blocks stay and take tiles off a counter: 40 prompts of unequal lengths and 4 heads are
+    more tiles than the device holds blocks, every one must be done exactly once (a tile done twice shows nowhere, so
+    the output starts as NaN and a tile left out stays NaN), and three launches in a row on the same counter agree."""
+    dtype, n_heads, n_kv_heads, head_dim = torch.bfloat16, 4, 2, 128
+    generator = np.random.default_rng(17)
+    lengths = [int(v) for v in generator.integers(1, 400, size=40)]
+    new_counts = [length if index % 3 else max(1, length // 2) for index, length in enumerate(lengths)]   # a third of them continue
+    keys, values, rows, positions, token_seq = paged_setup(lengths, new_counts, n_kv_heads, head_dim, dtype, seed=92, pages=sum((l + 63) // 64 for l in lengths) + 3)
+    tokens = positions.shape[0]
+    assert (tokens // 128 + len(lengths)) * n_heads > 2 * kernels.sm_count(DEVICE)
+    queries = randn(tokens, n_heads * head_dim, dtype=dtype, seed=93)
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(new_counts)]), dtype=torch.int32, device=DEVICE)
+    starts = torch.tensor([l - n for l, n in zip(lengths, new_counts)], dtype=torch.int32, device=DEVICE)
+    wanted = torch.empty(tokens, n_heads * head_dim, dtype=dtype)
+    plain_kernels.attention_generic(queries.cpu(), keys.cpu(), values.cpu(), wanted, positions.cpu(), token_seq.cpu(), rows.cpu(),
+                                    n_heads, n_kv_heads, head_dim, head_dim ** -0.5, 0)
+    results = []
+    for _ in range(3):
+        found = torch.full_like(queries, float("nan"))
+        kernels.attention_prefill_tc(queries, keys, values, found, cu, starts, rows, n_heads, n_kv_heads, head_dim, head_dim ** -0.5, 0)
+        assert kernels.attention_prefill_tc_status(head_dim) == 0
+        close(found, wanted, dtype)
+        results.append(found)
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+    for schedule in kernels._prefill_schedule.values():
+        assert int(schedule.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_heads,n_kv_heads,head_dim", [(4, 2, 16), (8, 2, 128), (6, 1, 80)])
 def test_decode_attention_finds_a_far_key(dtype, n_heads, n_kv_heads, head_dim):
