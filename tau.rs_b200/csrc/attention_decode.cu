@@ -266,9 +266,12 @@ struct DecodePrepare {
     int write_cache;              // 0: another run wrote this position's key and value already
 };
 
+// A lane's share of a position's rotation coefficients: elements lane, lane + 32, ... of the half-width tables.
+constexpr int kRotationsPerLane = (D / 2 + 31) / 32;
+
 // One warp: per-head norm (rounded to bfloat16), rotation of the first `rotary_dim` elements in 32-bit, rounded again.
 __device__ __forceinline__ void prepare_head(const bf16* __restrict__ source, const float* __restrict__ weight, float eps,
-                                             const float* __restrict__ cos_row, const float* __restrict__ sin_row, int rotary_dim,
+                                             const float (&cosines)[kRotationsPerLane], const float (&sines)[kRotationsPerLane], int rotary_dim,
                                              bf16* __restrict__ target, int lane) {
     float inverse = 1.0f;
     if (weight) {
@@ -284,11 +287,15 @@ __device__ __forceinline__ void prepare_head(const bf16* __restrict__ source, co
         return weight ? __bfloat162float(__float2bfloat16_rn(value * inverse * weight[e])) : value;
     };
     const int half = rotary_dim / 2;
-    for (int j = lane; j < half; j += 32) {
-        const float first = normalized(j), second = normalized(j + half);
-        const float c = cos_row[j], s = sin_row[j];
-        target[j] = __float2bfloat16_rn(first * c - second * s);
-        target[j + half] = __float2bfloat16_rn(second * c + first * s);
+#pragma unroll
+    for (int i = 0; i < kRotationsPerLane; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+            const float first = normalized(j), second = normalized(j + half);
+            const float c = cosines[i], s = sines[i];
+            target[j] = __float2bfloat16_rn(first * c - second * s);
+            target[j + half] = __float2bfloat16_rn(second * c + first * s);
+        }
     }
     for (int e = rotary_dim + lane; e < D; e += 32) target[e] = __float2bfloat16_rn(normalized(e));
 }
@@ -308,7 +315,6 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
                           int n_heads, int n_kv_heads, int passes, float scale, int window, int splits, DecodePrepare prepare,
                           int clustered) {
     grid_dependents_launch();
-    grid_dependency_wait();
     __shared__ float merge_o[kWarps][GH][D];
     __shared__ float merge_ml[kWarps][GH][2];
     __shared__ float block_ml[GH][2];        // clustered: this block's maximum (log2 units) and sum per head
@@ -321,7 +327,24 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
     const int group = n_heads / n_kv_heads;
     const int head0 = kv_head * group + pass * GH;
     const int heads_here = min(GH, group - pass * GH);
+    // What the step brought with it (lengths, page rows) and the tables were there before the step's first kernel began,
+    // so they are read while the kernel before this one is still at work: the newest position's page and this lane's
+    // rotation coefficients are here when that kernel's projection is.
     const int length = seq_len[seq];
+    int newest_page = 0;
+    float cosines[kRotationsPerLane], sines[kRotationsPerLane];
+    if (prepare.projected != nullptr && length > 0) {
+        newest_page = page_rows[static_cast<size_t>(seq) * page_stride + (length - 1) / page_tokens];
+#pragma unroll
+        for (int i = 0; i < kRotationsPerLane; ++i) {
+            const int j = lane + 32 * i;
+            const bool live = j < prepare.rotary_dim / 2;
+            const size_t place = static_cast<size_t>(length - 1) * (prepare.rotary_dim / 2) + j;
+            cosines[i] = live ? prepare.cos_table[place] : 1.0f;
+            sines[i] = live ? prepare.sin_table[place] : 0.0f;
+        }
+    }
+    grid_dependency_wait();
     const int first = (window > 0 && length > window) ? length - window : 0;
     const int span = length - first;
     const int per_split = ((span + splits - 1) / splits + 31) / 32 * 32;
@@ -338,16 +361,13 @@ decode_partial_mma_kernel(const bf16* __restrict__ queries, bf16* __restrict__ k
         // Every pass needs the newest row, so every pass whose range holds it writes it (the same values) and reads its own.
         const bool owns_newest = prepare.write_cache && lo <= position && position < hi;
         const bf16* row = prepare.projected + static_cast<size_t>(seq) * prepare.projected_stride;
-        const float* cos_row = prepare.rotary_dim ? prepare.cos_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
-        const float* sin_row = prepare.rotary_dim ? prepare.sin_table + static_cast<size_t>(position) * (prepare.rotary_dim / 2) : nullptr;
-        const size_t newest = (static_cast<size_t>(pages[position / page_tokens]) * n_kv_heads + kv_head) * head_stride +
-                              static_cast<size_t>(position % page_tokens) * D;
+        const size_t newest = (static_cast<size_t>(newest_page) * n_kv_heads + kv_head) * head_stride + static_cast<size_t>(position % page_tokens) * D;
         for (int task = warp; task < heads_here + (owns_newest ? 2 : 0); task += kWarps) {
             if (task < heads_here) {
-                prepare_head(row + static_cast<size_t>(head0 + task) * D, prepare.q_weight, prepare.eps, cos_row, sin_row, prepare.rotary_dim,
+                prepare_head(row + static_cast<size_t>(head0 + task) * D, prepare.q_weight, prepare.eps, cosines, sines, prepare.rotary_dim,
                              q_shared[task], lane);
             } else if (task == heads_here) {
-                prepare_head(row + static_cast<size_t>(n_heads + kv_head) * D, prepare.k_weight, prepare.eps, cos_row, sin_row,
+                prepare_head(row + static_cast<size_t>(n_heads + kv_head) * D, prepare.k_weight, prepare.eps, cosines, sines,
                              prepare.rotary_dim, keys + newest, lane);
             } else {
                 const bf16* source = row + static_cast<size_t>(n_heads + n_kv_heads + kv_head) * D;
