@@ -399,7 +399,10 @@ def main() -> int:
         clocks = ClockSampler() if sample_clocks else None
         if clocks:
             clocks.start()
-            time.sleep(0.3)
+        # The prompts' prefill ran at the power cap and leaves the SM clock low for some dozens of steps; every decode
+        # timing waits the same 0.3 s before its timed steps, so that all of them are taken at the clocks of decoding.
+        torch.cuda.synchronize()
+        time.sleep(0.3)
         before = kernels.launch_count()
         per_class = None
         if classes:
