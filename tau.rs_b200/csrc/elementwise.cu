@@ -114,10 +114,24 @@ __global__ void __launch_bounds__(kNormThreads)
 rms_norm_vec_kernel(T* __restrict__ values, const T* __restrict__ branch, const int* __restrict__ rows, const float* __restrict__ weight,
                     T* __restrict__ out, int width, float eps) {
     grid_dependents_launch();
-    grid_dependency_wait();
     constexpr int n = Vec16<T>::n;
     __shared__ float scratch[33];
+    // The norm's weight is a parameter of the model and the row numbers came with the step, before its first kernel: both are
+    // read while the kernel before this one is still at work, so that nothing but the rows themselves is waited for afterwards.
     const int source_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    float w[ITEMS][n];
+#pragma unroll
+    for (int item = 0; item < ITEMS; ++item) {
+        const int column = (item * kNormThreads + threadIdx.x) * n;
+        if (column < width) {
+#pragma unroll
+            for (int i = 0; i < n; i += 4) {
+                const float4 part = *reinterpret_cast<const float4*>(weight + column + i);
+                w[item][i] = part.x; w[item][i + 1] = part.y; w[item][i + 2] = part.z; w[item][i + 3] = part.w;
+            }
+        }
+    }
+    grid_dependency_wait();
     const size_t base = static_cast<size_t>(source_row) * width;
     float kept[ITEMS][n];
     float squares = 0.0f;
@@ -143,14 +157,9 @@ rms_norm_vec_kernel(T* __restrict__ values, const T* __restrict__ branch, const 
     for (int item = 0; item < ITEMS; ++item) {
         const int column = (item * kNormThreads + threadIdx.x) * n;
         if (column < width) {
-            float w[n], scaled[n];
+            float scaled[n];
 #pragma unroll
-            for (int i = 0; i < n; i += 4) {
-                const float4 part = *reinterpret_cast<const float4*>(weight + column + i);
-                w[i] = part.x; w[i + 1] = part.y; w[i + 2] = part.z; w[i + 3] = part.w;
-            }
-#pragma unroll
-            for (int i = 0; i < n; ++i) scaled[i] = kept[item][i] * inverse * w[i];
+            for (int i = 0; i < n; ++i) scaled[i] = kept[item][i] * inverse * w[item][i];
             *reinterpret_cast<uint4*>(target + column) = pack16<T>(scaled);
         }
     }
