@@ -345,7 +345,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             auto take = [&]() { return static_cast<int>(atomicAdd(schedule, 1)); };
             int scan_seq = 0, scan_tiles = 0;   // the sequence of the last item, and the tiles of the sequences before it
             // Writes item `number` (-1: the end) to its place, once those who read the item two before it are done with it.
-            auto publish = [&](uint32_t k, int number) {
+            auto publish = [&](uint32_t k, int& number) {
                 if (k >= 2 && !barrier_wait(&shared->item_free[k & 1], ((k >> 1) - 1) & 1u, abort_flag)) return false;
                 Item item = {-1, 0, 0, 0, 0};
                 if (number >= 0) {
@@ -359,14 +359,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                         if (tile - scan_tiles < tiles_here) break;
                         scan_tiles += tiles_here;
                     }
-                    item.head = number % n_heads;
-                    item.seq = 0;   // a place of the grid behind the last tile, unless:
                     if (scan_seq < n_seqs) {
                         const int block = (n_new + BM - 1) / BM - 1 - (tile - scan_tiles);   // the last tiles of a sequence first
+                        item.head = number % n_heads;
                         item.seq = scan_seq;
                         item.row = row0 + block * BM;
                         item.rows_here = min(BM, n_new - block * BM);
                         item.position0 = seq_start[scan_seq] + block * BM;
+                    } else {
+                        number = -1;   // behind the last tile (the launch counts a ragged tile for every sequence): so are all that follow
                     }
                 }
                 shared->item[k & 1] = item;
