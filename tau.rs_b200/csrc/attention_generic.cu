@@ -115,7 +115,7 @@ __global__ void attention_prepare_vec_kernel(
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             cosines[i] = cos_table[table + i];
-            sines[i] = sin_table[table + i];
+            sines[i] = lane < 16 ? -sin_table[table + i] : sin_table[table + i];   // first half: x cos - partner sin; second half: x cos + partner sin
         }
     }
     // A warp takes the heads warp, warp + warps, ...; their vectors are asked for several at a time, so that the loads of
@@ -138,8 +138,8 @@ __global__ void attention_prepare_vec_kernel(
                 target = queries + (static_cast<size_t>(token) * n_heads + head) * head_dim;
                 weight = q_weight;
             } else {
-                const int kv_head = (head - n_heads) % n_kv_heads;
                 const bool is_key = head < n_heads + n_kv_heads;
+                const int kv_head = head - n_heads - (is_key ? 0 : n_kv_heads);
                 target = (is_key ? keys : values) + cache_base + static_cast<size_t>(kv_head) * page_tokens * head_dim;
                 weight = k_weight;
                 if (!is_key) {  // values are stored as projected
@@ -163,8 +163,7 @@ __global__ void attention_prepare_vec_kernel(
 #pragma unroll
                 for (int i = 0; i < PER; ++i) {
                     const float partner = __shfl_xor_sync(0xffffffffu, value[i], 16);
-                    // first half: x cos - partner sin; second half: x cos + partner sin
-                    result.v[i] = from_float<T>(lane < 16 ? value[i] * cosines[i] - partner * sines[i] : value[i] * cosines[i] + partner * sines[i]);
+                    result.v[i] = from_float<T>(value[i] * cosines[i] + partner * sines[i]);
                 }
             } else {
 #pragma unroll
