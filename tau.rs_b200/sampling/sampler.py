@@ -55,6 +55,7 @@ class Sampler:
     def __init__(self, params: SamplingParams = SamplingParams()):
         self.params = params
         self._pinned = {}
+        self._key_rings = {}
         self._next = 0
 
     def launch(self, logits: torch.Tensor, request_ids: Sequence[int], token_indices: Sequence[int]) -> Pending:
@@ -63,7 +64,7 @@ class Sampler:
         if self.params.temperature == 0.0:
             kernels.argmax(logits, result[0], result[1])
         else:
-            keys = torch.tensor([list(request_ids), list(token_indices)], dtype=torch.int32).to(logits.device)
+            keys = self._upload(logits.device, request_ids, token_indices)
             kernels.sample_gumbel(logits, result[0], result[1], 1.0 / self.params.temperature, self.params.seed, keys[0], keys[1])
         if logits.device.type != "cuda":
             return Pending(result, result, None)
@@ -79,6 +80,22 @@ class Sampler:
         done = torch.cuda.Event()
         done.record()
         return Pending(result, host, done)
+
+    def _upload(self, device, request_ids: Sequence[int], token_indices: Sequence[int]) -> torch.Tensor:
+        """The rows' request numbers and token indices on the device, `[2, rows]`.  From page-locked memory and without
+        waiting: a copy from ordinary memory would make the host wait for the stream, and with it for the step that the
+        generation loop has just put there to run while the host works."""
+        rows = len(request_ids)
+        if device.type != "cuda":
+            return torch.tensor([list(request_ids), list(token_indices)], dtype=torch.int32, device=device)
+        if (rows, device) not in self._key_rings:   # a place is used again four launches later: the copy out of it is long over
+            self._key_rings[(rows, device)] = [torch.empty((2, rows), dtype=torch.int32).pin_memory() for _ in range(4)]
+        ring = self._key_rings[(rows, device)]
+        host = ring[self._next % len(ring)]
+        view = host.numpy()
+        view[0, :] = request_ids
+        view[1, :] = token_indices
+        return host.to(device, non_blocking=True)
 
     def collect(self, pending: Pending) -> List[int]:
         """Blocks until the tokens of `pending` are on the host.  A row that held only NaN gives `NO_TOKEN`: whether that
