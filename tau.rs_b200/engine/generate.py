@@ -316,4 +316,17 @@ def _take(tokens, rows):
         return tokens[rows[0] : rows[-1] + 1]
     import torch
 
-    return tokens.index_select(0, torch.tensor(rows, dtype=torch.int64, device=tokens.device))
+    if tokens.device.type != "cuda":
+        return tokens.index_select(0, torch.tensor(rows, dtype=torch.int64, device=tokens.device))
+    # The row numbers go up from page-locked memory without waiting (a copy from ordinary memory would make the host wait
+    # for the stream, and with it for the step that runs ahead).  A place is used again eight calls later.
+    ring = _row_rings.setdefault(tokens.device, [[], 0])
+    if len(ring[0]) < 8 or ring[0][0].numel() < len(rows):
+        ring[0] = [torch.empty(max(256, 2 * len(rows)), dtype=torch.int64).pin_memory() for _ in range(8)]
+    host = ring[0][ring[1] % 8]
+    ring[1] += 1
+    host.numpy()[: len(rows)] = rows
+    return tokens.index_select(0, host[: len(rows)].to(tokens.device, non_blocking=True))
+
+
+_row_rings = {}   # device -> [page-locked buffers, calls so far]
