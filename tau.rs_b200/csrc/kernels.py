@@ -418,7 +418,17 @@ def decode_splits(n_seqs: int, max_len: int, kv_blocks: int = 8, sms: Optional[i
     splits = max(1, min(4 * sms // blocks, bucket // 64, 16 if bucket <= 8192 else 32))
     if 8 < splits <= 16 and blocks * splits > 2 * sms:
         splits = 8
+    # The splits of a (sequence, KV head) are one cluster, and clusters do not fill the last places of the machine: on 148 SMs
+    # (592 places) 576 blocks in clusters of 3, 6 or 8 and 560 in clusters of 7 took a second wave (9 sequences of 2,048
+    # positions: 31.1 us with 8 splits, 21.2 us with 7; 24 sequences: 59.6 us with 3, 44.6 us with 2), while 560 in clusters of 5
+    # and 512 in clusters of 8 and 576 in pairs were resident at once.  So pairs may fill 98% of the places, clusters of up to 5
+    # 95%, larger ones 87%.
+    while 1 < splits <= 16 and blocks * splits * 100 > 4 * sms * _CLUSTER_FILL[min(splits, 6)]:
+        splits -= 1
     return splits
+
+
+_CLUSTER_FILL = {2: 98, 3: 95, 4: 95, 5: 95, 6: 87}   # per cent of the machine's places that clusters of this size (6: and more) fill
 
 
 _decode_scratch = {}

@@ -336,10 +336,12 @@ def test_decode_split_rule_stays_within_what_the_kernel_and_the_machine_take():
                     assert 1 <= splits <= (16 if bucket <= 8192 else 32)
                     assert splits == 1 or (splits * 64 <= bucket and splits * blocks <= 4 * sms)
                     assert not (8 < splits <= 16) or blocks * splits <= 2 * sms
+                    assert not (1 < splits <= 16) or blocks * splits * 100 <= 4 * sms * (98 if splits == 2 else 95 if splits <= 5 else 87)   # clusters leave the last places empty
                     low = bucket // 2 + 1
                     assert decode_splits(n_seqs, low, kv_blocks, sms) == splits == decode_splits(n_seqs, bucket, kv_blocks, sms)
     assert decode_splits(8, 2049, 8, 148) == 8 and decode_splits(1, 2049, 8, 148) == 16 and decode_splits(64, 2049, 8, 148) == 1
-    assert decode_splits(8, 2049, 8, 132) == 8 and decode_splits(8, 2049, 8, 74) == 4
+    assert decode_splits(8, 2049, 8, 132) == 7 and decode_splits(8, 2049, 8, 74) == 4
+    assert [decode_splits(n, 2049, 8, 148) for n in (9, 10, 12, 14, 16, 24, 32, 36, 37)] == [7, 6, 5, 5, 4, 2, 2, 2, 1]
 
 
 def test_a_row_of_nan_is_an_error_only_for_a_request_that_is_still_going():
