@@ -26,8 +26,20 @@ def _pointer(tensor: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def _stream_handle() -> int:
+    """The current stream of the current device as a number.  Asked of torch's C layer where it offers that: the Python-level
+    `torch.cuda.current_stream()` costs several microseconds, and every launch asks."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
+    return torch.cuda.current_stream().cuda_stream
+
+
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return ctypes.c_void_p(_stream_handle())
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -482,7 +494,7 @@ def attention_decode(queries, keys, values, out, seq_len, page_rows, n_heads: in
     floats = library.tau_attention_decode_scratch(ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(splits))
     scratch = tickets = None
     if floats:
-        key = (out.device, torch.cuda.current_stream().cuda_stream)
+        key = (out.device, _stream_handle())
         scratch = _decode_scratch.get(key)
         if scratch is None or scratch.numel() < floats:
             scratch = _decode_scratch[key] = torch.empty(floats, dtype=torch.float32, device=out.device)
@@ -560,7 +572,7 @@ def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page
     _require(cu_seqlens.numel() == n_seqs + 1 and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
              and page_rows.shape[0] == n_seqs, "one run and one row of pages per sequence")
     library = build.load_library("attention_prefill_tc.cu", (f"TAU_HEAD_DIM={head_dim}",))
-    key = (out.device, torch.cuda.current_stream().cuda_stream)
+    key = (out.device, _stream_handle())
     schedule = _prefill_schedule.get(key)
     if schedule is None:   # zero once; the kernel leaves it at zero
         schedule = _prefill_schedule[key] = torch.zeros(2, dtype=torch.int32, device=out.device)
@@ -612,7 +624,7 @@ def _scratch_for(logits) -> torch.Tensor:
     library = build.load_library("sampling.cu")
     library.tau_select_scratch_words.restype = ctypes.c_longlong
     words = library.tau_select_scratch_words(ctypes.c_int(logits.shape[0]), ctypes.c_int(logits.shape[1]))
-    key = (logits.device, torch.cuda.current_stream().cuda_stream)
+    key = (logits.device, _stream_handle())
     scratch = _select_scratch.get(key)
     if scratch is None or scratch.numel() < words:   # zero once: the tickets at its start; the kernel leaves them at zero
         scratch = _select_scratch[key] = torch.zeros(max(words, 1 << 16), dtype=torch.int32, device=logits.device)
