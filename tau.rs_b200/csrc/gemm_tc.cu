@@ -1010,6 +1010,11 @@ TAU_EXPORT int tau_gemm_tc(int out_dtype, const void* x, const void* w, const fl
         const int feature_tiles = (N + BM - 1) / BM, tiles = feature_tiles * ((M + 255) / 256);
         if (choose_splits(M, tiles, (K + BK - 1) / BK, sm_count(), workspace_floats, 256 * BM) > 1) {
             paired = false;
+        } else if (token_box == 0 && M <= 1024 && ((N + 255) / 256) * ((M + 255) / 256) * 100 >= 54 * (sm_count() / 2)) {
+            // Pairs of SMs (256 x 256 tiles) as soon as their tiles fill a good half of the pairs: from there on they beat every
+            // tile on single SMs (a gated 24576 x 4096 product at 256 tokens: 53.7 us against 69.2 us in tiles of 128 tokens;
+            // 6144 x 4096 at 1,024 tokens: 44.9 us against 51.5 us in tiles of 192), below it they leave too many SMs idle
+            // (4096 x 12288 at 512 tokens, 32 tiles for 74 pairs: 62.7 us against 49.1 us).
         } else if (token_box == 0 && M <= 1024) {
             // Between the batches that are cut along K and the prompts that fill every SM several times, the token tile
             // decides how many SMs have work: 512 tokens of a 6144-feature product are 96 tiles of 256 tokens, but 144
